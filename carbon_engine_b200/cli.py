@@ -112,8 +112,8 @@ def cmd_tiny_model(a) -> int:
     from . import models  # noqa: F401
     from .config.qwen3 import Qwen3Config
     from .weights.loader import write_random_model
-    if a.arch not in ("qwen3", "munizen", "lunerax"):
-        raise SystemExit(f"--arch {a.arch}: qwen3, munizen and lunerax are built")
+    if a.arch not in ("qwen3", "munizen", "lunerax", "vamadra"):
+        raise SystemExit(f"--arch {a.arch}: qwen3, munizen, lunerax and vamadra are built")
     heads = a.heads or 4
     head_dim = a.head_dim or 16
     store = {"f32": torch.float32, "bf16": torch.bfloat16}.get(a.dtype)
@@ -125,6 +125,15 @@ def cmd_tiny_model(a) -> int:
         cfg = sketch_config(a.vocab, a.hidden, a.layers, heads, a.kv_heads or max(1, heads // 2), head_dim,
                             a.intermediate or 2 * a.hidden, window=a.mask_size, side_dim=a.side_dim, max_positions=a.max_positions,
                             eps=a.rms_norm_eps, rope_base=a.rope_theta)
+        print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
+        return 0
+    if a.arch == "vamadra":
+        # latent attention everywhere (the odd layers read the rows the layer before cached); the feed-forward alternates
+        # between dense and a mixture of experts with a shared expert
+        from .config.vamadra import sketch_config
+        cfg = sketch_config(a.vocab, a.hidden, a.layers, heads, head_dim, a.intermediate or 2 * a.hidden, experts=a.experts,
+                            top=a.top_experts, groups=(a.expert_groups, max(1, a.expert_groups // 2)),
+                            max_positions=a.max_positions, eps=a.rms_norm_eps, rope_base=a.rope_theta, yarn_factor=a.yarn_factor)
         print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
         return 0
     if a.arch == "munizen":
@@ -188,7 +197,11 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     t = sub.add_parser("tiny-model", help="write a small random model folder")
     t.add_argument("--out", required=True)
-    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen | lunerax")
+    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen | lunerax | vamadra")
+    t.add_argument("--experts", type=int, default=8, help="vamadra: experts of a mixture layer")
+    t.add_argument("--top-experts", type=int, default=2, help="vamadra: experts a token uses")
+    t.add_argument("--expert-groups", type=int, default=4, help="vamadra: groups the experts form (half of them stay eligible)")
+    t.add_argument("--yarn-factor", type=float, default=0.0, help="vamadra: stretch of the rotary frequencies (0: none)")
     t.add_argument("--side-dim", type=int, default=8, help="lunerax: width of the per-layer token input (0: none)")
     t.add_argument("--streams", type=int, default=2, help="munizen: residual streams (0: an ordinary residual)")
     t.add_argument("--mask-size", type=int, default=256, help="munizen: positions in a block of the attention mask; lunerax: the sliding window")

@@ -50,16 +50,16 @@ _SIGNATURES = {
     # src, src_stride, src_head, src_off, dst, dst_stride, dst_head, dst_off, dtype, cos, sin, positions, status,
     # T, H, dr, rd, max_pos, stream
     "ce_rope_part": (_i, [_p, _i, _i, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
-    # in, in_stride, in_head, W, out, out_stride, out_head, gate, gate_stride, dtype, M, H, N, K, stream
-    "ce_head_matmul": (_i, [_p, _i, _i, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
+    # in, in_stride, in_head, W, out, out_stride, out_head, gate, gate_stride, gate_head, dtype, M, H, N, K, stream
+    "ce_head_matmul": (_i, [_p, _i, _i, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
-    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, stream
-    "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p]),
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks, stream
+    "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p, _p]),
     # d, dv, q_stride, q_head, ldk, ldv, alias
     "ce_masked_attention_mma_supported": (_i, [_i] * 7),
     # q, k_pool, v_pool, gate, out, positions, seq_slot, q_start, block_table, tiles, status, n_tiles, n_tokens, nh, nkv, d, dv,
-    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, stream
-    "ce_masked_attention_mma": (_i, [_p] * 11 + [_i] * 16 + [_f, _f, _p]),
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks, stream
+    "ce_masked_attention_mma": (_i, [_p] * 11 + [_i] * 16 + [_f, _f, _p, _p]),
     "ce_gated_delta_prep_width": (_i, [_i, _i, _i, _i]),
     # proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, out_dtype, seq_of_token, seq_slot, q_start,
     # T, B, ld, off_conv, off_b, H, G, d, dv, K, eps, stage, stream
@@ -96,6 +96,15 @@ _SIGNATURES = {
     # q, k_pool, v_pool, gate, out, positions, seq_slot, q_start, block_table, tiles, status, n_tiles, nh, nkv, d, dv,
     # q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale, stream
     "ce_diff_attention_mma": (_i, [_p] * 11 + [_i] * 12 + [_f] * 4 + [_p]),
+    # z, ids, weights, sgate, T, ld, E, top, groups, keep, scale, stream
+    "ce_moe_route": (_i, [_p] * 4 + [_i] * 6 + [_f, _p]),
+    "ce_moe_max_tiles": (_i, [_i, _i, _i]),
+    # ids, n_pairs, top, E, BM, max_rows, row_token, pair_row, tile_expert, n_tiles, stream
+    "ce_moe_align": (_i, [_p] + [_i] * 5 + [_p] * 5),
+    # in, W, out, row_token, tile_expert, n_tiles, dtype, max_tiles, BM, N, K, ldi, ldo, act, n_rows, stream
+    "ce_moe_matmul": (_i, [_p] * 6 + [_i] * 9 + [_p]),
+    # rows, dtype, ld, pair_row, weights, shared, sgate, y, T, top, W, accumulate, stream
+    "ce_moe_combine": (_i, [_p, _i, _i] + [_p] * 5 + [_i] * 4 + [_p]),
     # proj, out, out_dtype, T, ld, off, L, stream
     "ce_tanh_cols": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
     # proj, zz, w0, a_bias, norm_w, prep, raw, state, out, out_dtype, seq_slot, q_start, T, B, ld, off_r, off_k, off_v,

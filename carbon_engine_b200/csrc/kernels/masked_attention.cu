@@ -75,7 +75,7 @@ __global__ void latent_prepare_kernel(LatentPrepArgs a) {
     // the query latent
     float ss = 0.f;
     for (int j = threadIdx.x; j < a.qr; j += blockDim.x) ss = fmaf(row[a.off_q + j], row[a.off_q + j], ss);
-    float inv = 1.0f / sqrtf(ce_block_sum(ss, scratch) / (float)a.qr + a.eps);
+    float inv = a.qr > 0 ? 1.0f / sqrtf(ce_block_sum(ss, scratch) / (float)a.qr + a.eps) : 0.f;    // qr 0: the queries are no latent
     for (int j = threadIdx.x; j < a.qr; j += blockDim.x)
         CeType<T>::store((T*)a.cq + (size_t)t * a.qr + j, row[a.off_q + j] * inv * a.wq[j]);
     if (!a.write_kv) return;
@@ -113,9 +113,9 @@ extern "C" int ce_latent_prepare(const float* proj, const float* wq, const float
                                  int off_kv, int r, int dr, int rd, int page_size, int max_pages, int num_pages, int max_pos,
                                  int write_kv, float eps, cudaStream_t stream) {
     if (T == 0) return CE_OK;
-    if (!proj || !wq || !wkv || !cq || !positions || !seq_of_token || !seq_slot || !status)
+    if (!proj || !positions || !seq_of_token || !seq_slot || !status || (qr > 0 && (!wq || !cq)))
         return ce_fail(CE_ERR_ARG, "ce_latent_prepare: null pointer");
-    if (write_kv && (!k_pool || !block_table)) return ce_fail(CE_ERR_ARG, "ce_latent_prepare: no cache to write to");
+    if (write_kv && (!k_pool || !block_table || !wkv)) return ce_fail(CE_ERR_ARG, "ce_latent_prepare: no cache to write to");
     if (rd < 0 || rd > dr || rd % 2 || (rd > 0 && (!cos_table || !sin_table)))
         return ce_fail(CE_ERR_SIZE, "ce_latent_prepare: %d rotated elements of %d", rd, dr);
     LatentPrepArgs a{proj, wq, wkv, cq, k_pool, cos_table, sin_table, positions, seq_of_token, seq_slot, block_table, status,
@@ -174,7 +174,8 @@ extern "C" int ce_rope_part(const void* src, int src_stride, int src_head, int s
 
 // ---------------------------------------------------------------------------------------------
 // A product per head: out[t, h*out_head + j] = sum_i in[t, h*in_head + i] * W[h, j, i]  (j < N, i < K), float32
-// sums in the order of i; optionally times sigmoid(gate[t, h*N + j]) (gate logits float32).  Tiles of 16 tokens x 64 outputs of one head.
+// sums in the order of i; optionally times sigmoid(gate[t, h*N + j]) (gate logits float32), or, with one gate a head
+// (gate_head), times sigmoid(gate[t, h]).  Tiles of 16 tokens x 64 outputs of one head.
 // ---------------------------------------------------------------------------------------------
 #define HM_TM 16
 #define HM_TN 64
@@ -183,7 +184,7 @@ extern "C" int ce_rope_part(const void* src, int src_stride, int src_head, int s
 template <typename T>
 __global__ void __launch_bounds__(256) head_matmul_kernel(const T* __restrict__ in, int in_stride, int in_head, const T* __restrict__ W,
                                                           T* __restrict__ out, int out_stride, int out_head, const float* __restrict__ gate,
-                                                          int gate_stride, int M, int N, int K) {
+                                                          int gate_stride, int gate_head, int M, int N, int K) {
     ce_pdl_begin();
     __shared__ float As[HM_TM][HM_TK + 1];
     __shared__ float Ws[HM_TN][HM_TK + 1];
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(256) head_matmul_kernel(const T* __restrict__ 
         int n = n0 + tn + 16 * j;
         if (n >= N) continue;
         float v = acc[j];
-        if (gate) v *= ma_sigmoid(gate[(size_t)m * gate_stride + (size_t)h * N + n]);
+        if (gate) v *= ma_sigmoid(gate[(size_t)m * gate_stride + (gate_head ? (size_t)h : (size_t)h * N + n)]);
         CeType<T>::store(out + (size_t)m * out_stride + (size_t)h * out_head + n, v);
     }
 }
@@ -236,7 +237,7 @@ template <bool FEW>
 __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat16* __restrict__ in, int in_stride, int in_head,
                                                                const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out,
                                                                int out_stride, int out_head, const float* __restrict__ gate,
-                                                               int gate_stride, int M, int N, int K) {
+                                                               int gate_stride, int gate_head, int M, int N, int K) {
     using namespace nvcuda;
     ce_pdl_begin();
     __shared__ __align__(32) __nv_bfloat16 As[HW_TM][HW_TK + 16];
@@ -282,9 +283,15 @@ __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat
         if (m >= M || n >= N) continue;
         float x = Cs[r][c], y = Cs[r][c + 1];
         if (gate) {
-            const float* g = gate + (size_t)m * gate_stride + (size_t)h * N + n;
-            x *= ma_sigmoid(g[0]);
-            y *= ma_sigmoid(g[1]);
+            if (gate_head) {
+                float gv = ma_sigmoid(gate[(size_t)m * gate_stride + h]);
+                x *= gv;
+                y *= gv;
+            } else {
+                const float* g = gate + (size_t)m * gate_stride + (size_t)h * N + n;
+                x *= ma_sigmoid(g[0]);
+                y *= ma_sigmoid(g[1]);
+            }
         }
         __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)m * out_stride + (size_t)h * out_head + n) = v;
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat
 }
 
 extern "C" int ce_head_matmul(const void* in, int in_stride, int in_head, const void* W, void* out, int out_stride, int out_head,
-                              const float* gate, int gate_stride, int dtype, int M, int H, int N, int K, cudaStream_t stream) {
+                              const float* gate, int gate_stride, int gate_head, int dtype, int M, int H, int N, int K, cudaStream_t stream) {
     if (M == 0 || H == 0 || N == 0) return CE_OK;
     if (!in || !W || !out || K <= 0) return ce_fail(CE_ERR_ARG, "ce_head_matmul: null pointer or K=%d", K);
     if (H > 65535 || (M + HM_TM - 1) / HM_TM > 65535) return ce_fail(CE_ERR_SIZE, "ce_head_matmul: %d heads, %d tokens", H, M);
@@ -302,16 +309,16 @@ extern "C" int ce_head_matmul(const void* in, int in_stride, int in_head, const 
         ce_note("head_matmul_wmma_kernel");
         if (M <= 16)
             ce_launch(head_matmul_wmma_kernel<true>, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W,
-                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
+                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, gate_head, M, N, K);
         else
             ce_launch(head_matmul_wmma_kernel<false>, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W,
-                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
+                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, gate_head, M, N, K);
         return ce_check_launch("ce_head_matmul");
     }
     dim3 grid((N + HM_TN - 1) / HM_TN, (M + HM_TM - 1) / HM_TM, H);
     ce_note("head_matmul_kernel");
-    if (dtype == CE_F32) ce_launch(head_matmul_kernel<float>, grid, 256, 0, stream, (const float*)in, in_stride, in_head, (const float*)W, (float*)out, out_stride, out_head, gate, gate_stride, M, N, K);
-    else if (dtype == CE_BF16) ce_launch(head_matmul_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
+    if (dtype == CE_F32) ce_launch(head_matmul_kernel<float>, grid, 256, 0, stream, (const float*)in, in_stride, in_head, (const float*)W, (float*)out, out_stride, out_head, gate, gate_stride, gate_head, M, N, K);
+    else if (dtype == CE_BF16) ce_launch(head_matmul_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, gate_head, M, N, K);
     else return ce_fail(CE_ERR_ARG, "ce_head_matmul: unknown dtype %d", dtype);
     return ce_check_launch("ce_head_matmul");
 }
@@ -336,6 +343,7 @@ struct MaskedAttnArgs {
     const int* seq_slot;
     const int* block_table;
     int* status;
+    const float* sinks;          // [nh] or null: exp(sinks[h]) joins the softmax's denominator, with no key and no value
     int T, nh, nkv, d, dv, q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first;
     float scale, softcap;
 };
@@ -412,7 +420,13 @@ __global__ void masked_attention_kernel(MaskedAttnArgs a) {
         __syncthreads();
     }
     T* orow = (T*)a.out + ((size_t)t * a.nh + h) * dv;
-    float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    float shrink = 1.0f;
+    if (a.sinks) {                       // the sink: one more term of the denominator, taken as it is (no scale, no cap)
+        float sk = a.sinks[h], m_all = fmaxf(m_run, sk);
+        shrink = m_run == -INFINITY ? 0.f : expf(m_run - m_all);
+        l_run = l_run * shrink + expf(sk - m_all);
+    }
+    float inv = l_run > 0.f ? shrink / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < MA_MAX_ACC; ++i) {
         int j = tid + i * MA_THREADS;
@@ -428,7 +442,7 @@ extern "C" int ce_masked_attention(const void* q, const void* k_pool, const void
                                    const int* positions, const int* seq_of_token, const int* seq_slot, const int* block_table,
                                    int* status, int T, int nh, int nkv, int d, int dv, int q_stride, int q_head, int ldk, int ldv,
                                    int gate_stride, int page_size, int max_pages, int num_pages, int window, int keep_first,
-                                   float scale, float softcap, cudaStream_t stream) {
+                                   float scale, float softcap, const float* sinks, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !seq_of_token || !seq_slot || !block_table || !status)
         return ce_fail(CE_ERR_ARG, "ce_masked_attention: null pointer");
@@ -436,7 +450,7 @@ extern "C" int ce_masked_attention(const void* q, const void* k_pool, const void
         return ce_fail(CE_ERR_SIZE, "ce_masked_attention: head sizes %d / %d", d, dv);
     if (nkv <= 0 || nh % nkv != 0) return ce_fail(CE_ERR_SIZE, "ce_masked_attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     if (ldk < d || ldv < dv || nh > 65535) return ce_fail(CE_ERR_SIZE, "ce_masked_attention: a pool's rows are shorter than a head");
-    MaskedAttnArgs a{q, k_pool, v_pool, gate, out, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
+    MaskedAttnArgs a{q, k_pool, v_pool, gate, out, positions, seq_of_token, seq_slot, block_table, status, sinks, T, nh, nkv, d, dv,
                      q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap};
     size_t smem = (d + MA_THREADS + 32) * sizeof(float) + MA_THREADS * sizeof(long long);
     dim3 grid(T, nh);

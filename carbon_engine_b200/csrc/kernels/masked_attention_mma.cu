@@ -41,6 +41,7 @@ struct MaskedMmaArgs {
     const int* block_table;
     const int* tiles;            // (sequence, first token of the tile within the sequence's tokens of the step), 64 tokens a tile
     int* status;
+    const float* sinks;          // [nh] or null: exp(sinks[h]) joins the softmax's denominator, with no key and no value
     int nh, nkv, d, dv, q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first;
     int pack;                    // heads of one key head a block takes (a power of two up to 16 that divides nh / nkv)
     int slice;                   // value columns a block takes (a multiple of 16)
@@ -322,6 +323,7 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 2)) masked_attent
                 }
             }
         }
+        m_a = big_a; m_b = big_b;            // what the merged sums are relative to (the sink below joins them)
     } else {
     if (tid < MM_BN) {
         s_page[0][tid] = page_of(k0_of(0), tid);
@@ -347,9 +349,18 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 2)) masked_attent
     }
     }
     const int cq = (lane & 3) * 2;
-    float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
     const size_t tok_a = (size_t)(t0 + ra / pack), tok_b = (size_t)(t0 + rb / pack);
     const int head_a = head0 + ra % pack, head_b = head0 + rb % pack;
+    float sh_a = 1.0f, sh_b = 1.0f;
+    if (a.sinks) {                       // the sink, in the base-2 domain like the running maxima; it is neither scaled nor capped
+        float sk_a = (ra < n_rows ? a.sinks[head_a] : 0.f) * log2e, sk_b = (rb < n_rows ? a.sinks[head_b] : 0.f) * log2e;
+        float big_a = fmaxf(m_a, sk_a), big_b = fmaxf(m_b, sk_b);
+        sh_a = m_a == -INFINITY ? 0.f : exp2f(m_a - big_a);
+        sh_b = m_b == -INFINITY ? 0.f : exp2f(m_b - big_b);
+        l_a = l_a * sh_a + exp2f(sk_a - big_a);
+        l_b = l_b * sh_b + exp2f(sk_b - big_b);
+    }
+    float i_a = l_a > 0.f ? sh_a / l_a : 0.f, i_b = l_b > 0.f ? sh_b / l_b : 0.f;
 #pragma unroll
     for (int nt = 0; nt < DVT; ++nt) {
         if (nt * 8 < ncol) {
@@ -430,7 +441,8 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
                                        const int* positions, const int* seq_slot, const int* q_start, const int* block_table,
                                        const int* tiles, int* status, int n_tiles, int n_tokens, int nh, int nkv, int d, int dv,
                                        int q_stride, int q_head, int ldk, int ldv, int gate_stride, int page_size, int max_pages,
-                                       int num_pages, int window, int keep_first, float scale, float softcap, cudaStream_t stream) {
+                                       int num_pages, int window, int keep_first, float scale, float softcap, const float* sinks,
+                                       cudaStream_t stream) {
     if (n_tiles == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !seq_slot || !q_start || !block_table || !tiles || !status)
         return ce_fail(CE_ERR_ARG, "ce_masked_attention_mma: null pointer");
@@ -457,7 +469,7 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
         if (mm_smem_bytes(d, slice, alias, 2) > 200 * 1024) slice = mm_slice(dv, 4);
     }
     MaskedMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
-                    (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride, q_head,
+                    (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, sinks, nh, nkv, d, dv, q_stride, q_head,
                     ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, buffers == 4, scale, softcap};
     dim3 grid(n_tiles * pack, nh / pack, (dv + slice - 1) / slice);
     size_t smem = mm_smem_bytes(d, slice, alias, buffers);

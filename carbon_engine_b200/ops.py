@@ -315,17 +315,20 @@ def latent_prepare(proj, wq, wkv, cq, k_pool, cos, sin, positions, seq_of_token,
                    qr: int, off_kv: int, r: int, dr: int, rd: int, page_size: int, eps: float, write_kv: bool = True) -> None:
     """Latent attention's operands from one float32 product row: cq = rms_norm(query latent) * wq; the token's
     cache row [rms_norm(latent) * wkv | rotated key part] into ``k_pool`` [pages, 1, page, r + dr]."""
-    _need(proj, "proj", torch.float32); _need(wq, "wq", torch.float32); _need(wkv, "wkv", torch.float32); _need(cq, "cq")
-    if cq.shape != (proj.shape[0], qr) or wq.numel() != qr or wkv.numel() != r:
+    _need(proj, "proj", torch.float32)
+    if qr > 0:
+        _need(wq, "wq", torch.float32); _need(cq, "cq")
+    if (qr > 0 and (cq.shape != (proj.shape[0], qr) or wq.numel() != qr)) or (write_kv and (wkv is None or wkv.numel() != r)):
         raise KernelError("latent_prepare: sizes do not fit")
     if write_kv:
-        _need(k_pool, "k_pool", cq.dtype)
+        _need(wkv, "wkv", torch.float32)
+        _need(k_pool, "k_pool", cq.dtype if qr > 0 else None)
         if tuple(k_pool.shape[1:]) != (1, page_size, r + dr):
             raise KernelError(f"latent_prepare: pool {tuple(k_pool.shape)} is not [pages, 1, {page_size}, {r + dr}]")
     if rd > 0 and (cos is None or cos.shape[1] != rd // 2):
         raise KernelError("latent_prepare: rotary table width is not rd / 2")
     _ok(kernels().ce_latent_prepare(
-        _ptr(proj), _ptr(wq), _ptr(wkv), _ptr(cq), _ptr(k_pool), dtype_code(cq.dtype), _ptr(cos), _ptr(sin), _ptr(positions),
+        _ptr(proj), _ptr(wq), _ptr(wkv), _ptr(cq), _ptr(k_pool), dtype_code(cq.dtype if qr > 0 else k_pool.dtype), _ptr(cos), _ptr(sin), _ptr(positions),
         _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status), proj.shape[0], proj.stride(0), int(off_q), int(qr),
         int(off_kv), int(r), int(dr), int(rd), int(page_size), block_table.shape[1] if block_table is not None else 0,
         k_pool.shape[0] if k_pool is not None else 0, cos.shape[0] if cos is not None else 0, 1 if write_kv else 0, float(eps),
@@ -342,9 +345,10 @@ def rope_part(src, src_head: int, src_off: int, dst, dst_head: int, dst_off: int
                                src.shape[0], int(heads), int(dr), int(rd), cos.shape[0] if cos is not None else 0, _stream()))
 
 
-def head_matmul(inp, in_head: int, w, out, out_head: int, heads: int, n: int, k: int, gate=None) -> None:
+def head_matmul(inp, in_head: int, w, out, out_head: int, heads: int, n: int, k: int, gate=None, gate_per_head: bool = False) -> None:
     """out[t, h*out_head + j] = sum_i inp[t, h*in_head + i] * w[h, j, i] (j < n, i < k), optionally times
-    sigmoid(gate[t, h*n + j]) (float32 logits); w [heads, n, k] contiguous, operands and output in one dtype."""
+    sigmoid(gate[t, h*n + j]) or, with ``gate_per_head``, sigmoid(gate[t, h]) (float32 logits); w [heads, n, k]
+    contiguous, operands and output in one dtype."""
     _need(w, "w", inp.dtype)
     if tuple(w.shape) != (heads, n, k) or out.dtype != inp.dtype or inp.stride(-1) != 1 or out.stride(-1) != 1:
         raise KernelError("head_matmul: shapes or dtypes do not fit")
@@ -355,25 +359,32 @@ def head_matmul(inp, in_head: int, w, out, out_head: int, heads: int, n: int, k:
         M = inp.shape[0]
         prof.note_work((M * heads * (n + k) + heads * n * k) * inp.element_size(), 2 * M * heads * n * k)
     _ok(kernels().ce_head_matmul(_ptr(inp), inp.stride(0), int(in_head), _ptr(w), _ptr(out), out.stride(0), int(out_head),
-                                 _ptr(gate), gate.stride(0) if gate is not None else 0, dtype_code(inp.dtype), inp.shape[0],
+                                 _ptr(gate), gate.stride(0) if gate is not None else 0, 1 if gate_per_head else 0,
+                                 dtype_code(inp.dtype), inp.shape[0],
                                  int(heads), int(n), int(k), _stream()))
 
 
 def masked_attention(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_of_token, seq_slot,
                      block_table, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int, keep_first: int,
-                     scale: float, softcap: float) -> None:
+                     scale: float, softcap: float, sinks=None) -> None:
     """Softmax attention in float32 arithmetic with separate key and value head sizes, a tanh cap on the scores
     (0: none), a window (0: none) that keeps the first ``keep_first`` keys visible, and an optional sigmoid gate per
     output element.  ``v_pool`` may be the key pool itself (``ldv`` = ``ldk``): the values are then the leading
-    ``dv`` elements of every key row."""
+    ``dv`` elements of every key row.  ``sinks`` (float32 [nh]): exp(sinks[h]) is one more term of head h's denominator."""
     _need(k_pool, "k_pool"); _need(out, "out", k_pool.dtype)
+    _check_sinks(sinks, nh)
     if q.dtype != k_pool.dtype or v_pool.dtype != k_pool.dtype:
         raise KernelError("masked_attention: q and the cache differ in dtype")
     _ok(kernels().ce_masked_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), dtype_code(out.dtype), _ptr(positions), _ptr(seq_of_token),
         _ptr(seq_slot), _ptr(block_table), _ptr(status), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
         gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
-        float(scale), float(softcap), _stream()))
+        float(scale), float(softcap), _ptr(sinks), _stream()))
+
+
+def _check_sinks(sinks, nh: int) -> None:
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh or not sinks.is_contiguous() or not sinks.is_cuda):
+        raise KernelError(f"attention sinks must be {nh} float32 numbers on the GPU")
 
 
 def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, ldk: int, ldv: int, alias: bool) -> bool:
@@ -382,17 +393,18 @@ def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, 
 
 def masked_attention_mma(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_slot, q_start, block_table,
                          tiles, n_tiles: int, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int,
-                         keep_first: int, scale: float, softcap: float) -> None:
+                         keep_first: int, scale: float, softcap: float, sinks=None) -> None:
     """:func:`masked_attention` on the tensor cores (bfloat16) for tiles of 64 query tokens: ``tiles`` holds (sequence, first
     token within the sequence's tokens of the step) pairs.  ``gate`` holds bfloat16 logits."""
     _need(k_pool, "k_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
     if q.dtype != torch.bfloat16 or v_pool.dtype != torch.bfloat16 or (gate is not None and gate.dtype != torch.bfloat16):
         raise KernelError("masked_attention_mma: bfloat16 only")
+    _check_sinks(sinks, nh)
     _ok(kernels().ce_masked_attention_mma(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), _ptr(positions), _ptr(seq_slot), _ptr(q_start), _ptr(block_table),
         _ptr(tiles), _ptr(status), int(n_tiles), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
         gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
-        float(scale), float(softcap), _stream()))
+        float(scale), float(softcap), _ptr(sinks), _stream()))
 
 
 def gated_delta_prep_width(heads: int, key_heads: int, d: int, dv: int) -> int:
@@ -626,6 +638,84 @@ def general_delta(proj, zz, w0, a_bias, norm_w, prep, raw, state, out, seq_slot,
         _ok(kernels().ce_general_delta(_ptr(proj), _ptr(zz), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(prep), _ptr(raw),
                                        _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), T, n_seqs,
                                        proj.stride(0), off_r, off_k, off_v, off_a, off_g, heads, d, float(eps), stage, _stream()))
+
+
+MOE_ACTIVATIONS = {"none": 0, "relu2": 1}
+
+
+def moe_route(z: torch.Tensor, experts: int, top: int, groups: int, keep: int, scale: float, ids: torch.Tensor,
+              weights: torch.Tensor, sgate: Optional[torch.Tensor] = None) -> None:
+    """Router logits z [T, >= experts (+1)] float32 -> the ``top`` experts of every token (``ids`` int32 [T, top], best
+    first) and their weights (float32 [T, top]): softmax over the experts, experts in ``groups`` equal groups of neighbours
+    of which the ``keep`` with the largest member stay eligible, weights = chosen scores / their sum * scale.  With
+    ``sgate`` (float32 [T]) column ``experts`` of z is a gate logit: sgate = sigmoid of it."""
+    _need(z, "z", torch.float32); _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32)
+    T = z.shape[0]
+    if ids.shape != (T, top) or weights.shape != (T, top) or (sgate is not None and (sgate.dtype != torch.float32 or sgate.numel() != T)):
+        raise KernelError("moe_route: sizes do not fit")
+    _ok(kernels().ce_moe_route(_ptr(z), _ptr(ids), _ptr(weights), _ptr(sgate), T, z.stride(0), int(experts), int(top), int(groups),
+                               int(keep), float(scale), _stream()))
+
+
+def moe_max_tiles(n_pairs: int, experts: int, tile: int) -> int:
+    """The most tiles of ``tile`` rows that ``n_pairs`` (token, expert) pairs can fill when every expert's rows start a tile."""
+    return n_pairs // tile + min(n_pairs, experts)
+
+
+def moe_align(ids: torch.Tensor, experts: int, tile: int, row_token: torch.Tensor, pair_row: torch.Tensor,
+              tile_expert: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Lay the pairs of ``ids`` [T, top] out by expert: ``row_token`` [rows] (the token of a row, -1 for padding),
+    ``pair_row`` [T * top], ``tile_expert`` [tiles], ``n_tiles`` [1]; all int32 on the device."""
+    for t, name in ((ids, "ids"), (row_token, "row_token"), (pair_row, "pair_row"), (tile_expert, "tile_expert"), (n_tiles, "n_tiles")):
+        _need(t, name, torch.int32)
+    n = ids.numel()
+    if pair_row.numel() < n or tile_expert.numel() * tile > row_token.numel() or tile_expert.numel() < moe_max_tiles(n, experts, tile):
+        raise KernelError("moe_align: the layout's tables are too small")
+    _ok(kernels().ce_moe_align(_ptr(ids), n, ids.shape[1], int(experts), int(tile), row_token.numel(), _ptr(row_token),
+                               _ptr(pair_row), _ptr(tile_expert), _ptr(n_tiles), _stream()))
+
+
+def moe_matmul(inp: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile: int, activation: str = "none", row_token=None,
+               tile_expert=None, n_tiles=None) -> None:
+    """out[p] = act(inp[row_token[p]] @ w[tile_expert[p // tile]].T) for the rows of the layout's tiles (``row_token``
+    None: the input rows are the layout's rows already).  Without any table: out = act(inp @ w[0].T), row by row.
+    w [experts, N, K]; operands and output in one dtype."""
+    _need(w, "w", inp.dtype); _need(out, "out", inp.dtype)
+    if inp.stride(-1) != 1 or w.dim() != 3 or inp.shape[1] != w.shape[2] or out.shape[1] != w.shape[1]:
+        raise KernelError("moe_matmul: shapes do not fit")
+    if tile_expert is None:
+        rows = inp.shape[0]
+        tiles = (rows + tile - 1) // tile
+        if out.shape[0] < rows:
+            raise KernelError("moe_matmul: the output has fewer rows than the input")
+    else:
+        rows, tiles = out.shape[0], tile_expert.numel()
+        if out.shape[0] < tiles * tile or (row_token is None and inp.shape[0] < tiles * tile):
+            raise KernelError("moe_matmul: the layout has more rows than the operands")
+    prof = profiling()
+    if prof is not None:
+        # what a step of this size moves and computes when every tile is full: the rows in and out, and the experts' weights
+        # (each read once, at most as many as there are tiles)
+        live = min(w.shape[0], max(tiles, 1))
+        n_rows = min(rows, tiles * tile)
+        prof.note_work((n_rows * (w.shape[1] + w.shape[2]) + live * w.shape[1] * w.shape[2]) * inp.element_size(),
+                       2 * n_rows * w.shape[1] * w.shape[2])
+    _ok(kernels().ce_moe_matmul(_ptr(inp), _ptr(w), _ptr(out), _ptr(row_token), _ptr(tile_expert), _ptr(n_tiles), dtype_code(inp.dtype),
+                                tiles, int(tile), w.shape[1], w.shape[2], inp.stride(0), out.stride(0), MOE_ACTIVATIONS[activation],
+                                rows, _stream()))
+
+
+def moe_combine(rows: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, y: torch.Tensor, shared=None, sgate=None,
+                accumulate: bool = False) -> None:
+    """y[t] (+)= sum_k weights[t, k] * rows[pair_row[t * top + k]] (+ sgate[t] * shared[t]); y float32 [T, W]."""
+    _need(y, "y", torch.float32); _need(weights, "weights", torch.float32); _need(pair_row, "pair_row", torch.int32)
+    T, top = weights.shape
+    if y.shape[0] != T or rows.shape[1] != y.shape[1] or rows.stride(-1) != 1 or pair_row.numel() < T * top:
+        raise KernelError("moe_combine: sizes do not fit")
+    if shared is not None and (shared.dtype != rows.dtype or shared.shape != y.shape or not shared.is_contiguous()):
+        raise KernelError("moe_combine: the shared expert's rows must be [T, W] in the experts' dtype")
+    _ok(kernels().ce_moe_combine(_ptr(rows), dtype_code(rows.dtype), rows.stride(0), _ptr(pair_row), _ptr(weights), _ptr(shared),
+                                 _ptr(sgate), _ptr(y), T, top, y.shape[1], 1 if accumulate else 0, _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

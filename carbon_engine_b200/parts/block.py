@@ -1,11 +1,12 @@
 """Arrangements of parts in a layer.  Pre-norm: x += mixer(norm1(x)); x += ffn(norm2(x))
-(src/model/mod.rs:645-650)."""
+(src/model/mod.rs:645-650).  Output-norm: x += norm1(mixer(x)); x += norm2(ffn(x))."""
 from __future__ import annotations
 
 from typing import List, Optional
 
 import torch
 
+from .. import ops
 from .base import Block, BundleCacheSpec, FeedForward, Mixer, Norm, Part
 
 
@@ -36,6 +37,50 @@ class PreNormBlock(Block):
             self.ffn.forward(ctx, h, x)
         if self.after is not None:
             self.after.forward(ctx, x)
+
+
+class OutputNormBlock(Block):
+    """The norm sits on each sublayer's OUTPUT: x += norm1(mixer(x)); x += norm2(ffn(x)).  The sublayers read the
+    residual itself, rounded to the compute dtype (in float32 they read it in place).  The sublayers STORE their result
+    in a float32 buffer (``can_store``), and the norm's kernel adds its normalised rows into the residual."""
+
+    def __init__(self, width: int, mixer: Mixer, mixer_norm: Norm, ffn: Optional[FeedForward] = None, ffn_norm: Optional[Norm] = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        for part in (mixer, ffn):
+            if part is not None and not getattr(part, "can_store", False):
+                raise ValueError(f"{type(part).__name__} cannot store its output, which a norm on the output needs")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and not hasattr(norm, "add_into"):
+                raise ValueError(f"{type(norm).__name__} cannot add its output into the residual")
+        self.width, self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = int(width), mixer, mixer_norm, ffn, ffn_norm
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        ffn = self.ffn.step_bytes(tokens, element_size) if self.ffn is not None else 0
+        return tokens * self.width * (element_size + 4) + max(self.mixer.step_bytes(tokens, element_size), ffn)
+
+    def _read(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        if ctx.dtype == torch.float32:
+            return x
+        h = ctx.buffer(tuple(x.shape))
+        ops.copy_cols(x, 0, x.shape[1], h)
+        return h
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> None:
+        y = ctx.buffer(tuple(x.shape), torch.float32)
+        owed = self.mixer.forward(ctx, self._read(ctx, x), y, cache, accumulate=False)
+        if owed is not None:
+            ops.add_bias(y, owed)
+        self.mixer_norm.add_into(y, x)
+        if self.ffn is None:
+            return
+        owed = self.ffn.forward(ctx, self._read(ctx, x), y, accumulate=False)
+        if owed is not None:
+            ops.add_bias(y, owed)
+        self.ffn_norm.add_into(y, x)
 
 
 class StreamBlock(Block):

@@ -14,6 +14,7 @@ from .gated_delta import ChannelGatedDelta
 from .latent_attention import LatentAttention
 from .masked_attention import GatedWindowAttention
 from .mlp import GatedMLP
+from .moe import RoutedExperts
 from .norm import GroupedRMSNorm, LayerNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 
@@ -53,6 +54,7 @@ register_mixer("gated_window_attention", GatedWindowAttention)
 register_mixer("latent_attention", LatentAttention)
 register_mixer("channel_gated_delta", ChannelGatedDelta)
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("routed_experts", RoutedExperts)
 register_norm("rmsnorm", RMSNorm)
 register_norm("grouped_rmsnorm", GroupedRMSNorm)
 register_norm("layernorm", LayerNorm)

@@ -64,11 +64,10 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling: Optional[RopeScaling] 
             return dim * math.log(scaling.original_max_position / (rotations * 2.0 * math.pi)) / (2.0 * math.log(theta))
         low = max(math.floor(correction(scaling.beta_fast)), 0.0)
         high = min(math.ceil(correction(scaling.beta_slow)), dim - 1.0)
-        if high == low:
-            high += 0.001
+        span = max(high - low, 0.001)
         out = []
         for i, f in enumerate(inv):
-            ramp = min(max((i - low) / (high - low), 0.0), 1.0)
+            ramp = min(max((i - low) / span, 0.0), 1.0)
             keep = 1.0 - ramp                                   # 1: the frequency stays, 0: it is divided
             out.append(f / scaling.factor * (1.0 - keep) + f * keep)
         return out
