@@ -190,15 +190,36 @@ def lunerax_config(width, heads, kv_heads, ff, layers, vocab):
                                     "token_side": {"dim": 128}, "max_position_embeddings": 8192})
 
 
+def vamadra_config(width, heads, kv_heads, ff, layers, vocab):
+    """A Vamadra model at the Qwen3 model's layer sizes: every layer latent attention with the Lunerax latent layer's sizes
+    (heads of 128 + 32, values of 128, a cached row of 256 + 32 per token; no window), a sink and a gate per head, stretched
+    rotary frequencies; of every two layers the second reads the rows the first cached.  The feed-forward alternates between
+    the dense one and a mixture of 32 experts in 4 groups (2 kept), 4 per token, each an eighth of the dense width, beside a
+    shared expert of half the dense width: a token's products are as wide as the dense layer's."""
+    from carbon_engine_b200.config.vamadra import VamadraConfig
+    rotation = {"dims": 32, "base": 1e6, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    out = []
+    for i in range(layers):
+        m = {"heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "kv_rank": 256, "scale": 160 ** -0.5, "rot": rotation}
+        if i % 2:
+            m["kv_from"] = i - 1
+        mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else {
+            "kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 2},
+            "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}, "scale": 2.5}}
+        out.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return VamadraConfig.from_dict({"architecture": "Vamadra", "vocab": vocab, "width": width, "layers": out,
+                                    "norm": {"eps": 1e-6}, "max_position_embeddings": 8192})
+
+
 def compare_designs(args, BenchHarness, pk) -> int:
-    """Prefill and decode throughput of the engine's other designs (--designs: munizen, lunerax) beside the Qwen3 dense
+    """Prefill and decode throughput of the engine's other designs (--designs: munizen, lunerax, vamadra) beside the Qwen3 dense
     design at equal layer sizes (random weights, a few layers), with the kernels of each and their distance from the roofline."""
     import torch
-    makers = {"munizen": munizen_config, "lunerax": lunerax_config}
+    makers = {"munizen": munizen_config, "lunerax": lunerax_config, "vamadra": vamadra_config}
     designs = [x for x in args.designs.split(",") if x != "qwen3"]
     for x in designs:
         if x not in makers:
-            raise SystemExit(f"--designs {x}: munizen, lunerax and qwen3 are built")
+            raise SystemExit(f"--designs {x}: munizen, lunerax, vamadra and qwen3 are built")
     layers = args.layers if args.layers != SIZES_8B["num_hidden_layers"] else 4
     vocab, out = 32768, {}
     for name in args.sizes.split(","):
@@ -257,9 +278,9 @@ def main() -> int:
     ap.add_argument("--sizes", default="1b,8b", help="with --workload compare-designs: which of the layer sizes "
                     "1b, 4b, 8b (width / heads / feed-forward of models of about that size), with commas between them")
     ap.add_argument("--designs", default="munizen,qwen3", help="with --workload compare-designs: the designs set beside one another "
-                    "(munizen, lunerax; qwen3 is always the last)")
+                    "(munizen, lunerax, vamadra; qwen3 is always the last)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b", "compare-designs"],
-                    help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
+                    help="decode: the headline line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
                          "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "
                          "tokens each.  batch16-32b: 16 prompts of 1,024 tokens at Qwen3-32B sizes, 256 new tokens each.  Both "
                          "run through the scheduler and print a line of their own.  compare-designs: prefill and decode throughput of "

@@ -103,6 +103,8 @@ _SIGNATURES = {
     "ce_moe_align": (_i, [_p] + [_i] * 5 + [_p] * 5),
     # in, W, out, row_token, tile_expert, n_tiles, dtype, max_tiles, BM, N, K, ldi, ldo, act, n_rows, stream
     "ce_moe_matmul": (_i, [_p] * 6 + [_i] * 9 + [_p]),
+    # in, ldi, K, elsize, row_token, n_tiles, BM, out, max_rows, stream
+    "ce_moe_gather": (_i, [_p, _i, _i, _i, _p, _p, _i, _p, _i, _p]),
     # rows, dtype, ld, pair_row, weights, shared, sgate, y, T, top, W, accumulate, stream
     "ce_moe_combine": (_i, [_p, _i, _i] + [_p] * 5 + [_i] * 4 + [_p]),
     # proj, out, out_dtype, T, ld, off, L, stream

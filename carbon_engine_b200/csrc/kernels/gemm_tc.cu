@@ -538,6 +538,158 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
 
 
 // ---------------------------------------------------------------------------------------------
+// Grouped product (mixture of experts): the rows of x lie in tiles of BN rows, every tile belongs to ONE expert
+// (tile_expert[j]; tiles from n_tiles[0] on are empty and their blocks leave at once, so a launch sized for the most
+// tiles a step can have serves any routing), and W is the stack [experts, N, K] read as one matrix [experts * N, K].
+// A block takes 128 output features of one tile: the same roles and pipeline as the kernel above, without split-K.
+// Where N is no multiple of 128 the last box of an expert reaches into the next expert's rows (or past the stack's
+// end, which reads zeros): those features are not stored.  Without tables it is one expert's product over the rows as
+// they lie.  Epilogue: store in bfloat16, optionally the square of relu first.
+// ---------------------------------------------------------------------------------------------
+struct TcGroupArgs {
+    __nv_bfloat16* out;          // [rows, ldo]
+    const int* tile_expert;      // [tiles] or null
+    const int* n_tiles;          // [1] or null
+    int* status;
+    int rows, N, K, ldo, kblocks, act;       // act 1: relu(v)^2
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 2) gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                 const __grid_constant__ CUtensorMap map_x, TcGroupArgs a, int stages) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_acc_ok;
+    constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // the layout's tables are written by the kernels before this one: nothing is read before they are complete
+    ce_pdl_launch_dependents();
+    ce_pdl_wait();
+    const int tile = blockIdx.y;
+    int expert = 0;
+    if (a.tile_expert) {
+        if (tile >= a.n_tiles[0]) return;                  // the whole block leaves: nothing is allocated yet
+        expert = a.tile_expert[tile];
+    }
+    const int n0 = blockIdx.x * BM, m0 = tile * BN;
+    const int w_row0 = expert * a.N + n0;
+    const int nkb = a.kblocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer
+            int issued = 0, s = 0;
+            uint32_t eph = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                if (i >= stages) {
+                    ok = mbar_wait(&empty_bar[s], eph);
+                    if (!ok) break;
+                }
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(st, &map_w, &full_bar[s], i * BK, w_row0);
+                tma_load_2d(st + W_BYTES, &map_x, &full_bar[s], i * BK, m0);
+                issued = i + 1;
+                if (++s == stages) { s = 0; if (i >= stages) eph ^= 1; }
+            }
+            if (!ok) {
+                atomicExch(a.status, 5);
+                for (int i = max(0, issued - stages); i < issued; ++i) mbar_wait(&full_bar[i % stages], (i / stages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
+            const uint64_t desc_hi = umma_desc(0);
+            for (int i = 0; i < nkb; ++i) {
+                ok = mbar_wait(&full_bar[s], ph);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t st = (base + s * STAGE_BYTES) >> 4;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    uint64_t bdesc = desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
+                    uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                    umma_bf16(tmem, desc_hi | (uint64_t)((st + ((kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
+                }
+                umma_commit(&empty_bar[s]);
+                if (++s == stages) { s = 0; ph ^= 1; }
+            }
+            if (ok) umma_commit(&acc_bar);
+            else atomicExch(a.status, 5);
+        }
+    } else {
+        // ---- epilogue: 4 warps, each reads the 32 accumulator lanes of its quadrant
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int n = n0 + row;
+        const int m_valid = min(BN, a.rows - m0);
+        if (threadIdx.x == 64) {
+            bool there = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
+            if (!there) atomicExch(a.status, 5);
+            s_acc_ok = there ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool ok = s_acc_ok != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= m_valid) break;
+                float g[16];
+                if (nkb > 0) tmem_ld16(taddr + c, g);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = 0.f;
+                }
+                if (n < a.N) {
+                    __nv_bfloat16* op = a.out + (size_t)(m0 + c) * a.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float v = g[j];
+                        if (a.act == 1) { v = fmaxf(v, 0.f); v = v * v; }
+                        if (c + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------
 // Many tokens (prefill): a persistent kernel.  One CTA per SM walks over output tiles (tokens
 // fastest, so the CTAs that run together share weight tiles in L2); tensor memory holds two sets of
 // accumulators, so the epilogue of one tile runs while the MMAs of the next fill the other set.
@@ -1238,4 +1390,52 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     }
 #undef TC_CASE
     return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: no tile for M=%d", M);
+}
+
+// ---- grouped product over a layout by expert -------------------------------------------------------------------
+namespace {
+template <int BN>
+int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, const TcGroupArgs& a, dim3 grid, cudaStream_t stream) {
+    constexpr size_t stage = BM * BK * 2 + BN * BK * 2;
+    int stages = (int)((100 * 1024) / stage);          // two blocks an SM
+    if (stages > 8) stages = 8;
+    size_t smem = stages * stage + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc_grouped: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    ce_note("gemm_tc_grouped_kernel");
+    ce_launch(gemm_tc_grouped_kernel<BN>, grid, THREADS, smem, stream, mw, mx, a, stages);
+    return ce_check_launch("ce_gemm_tc_grouped");
+}
+}  // namespace
+
+extern "C" int ce_gemm_tc_grouped_supported(int tile, int N, int K, int ldi, int ldo) {
+    return (tile == 64 || tile == 128) && N > 0 && K > 0 && K % 8 == 0 && ldi % 8 == 0 && ldo > 0;
+}
+
+// x [x_rows, ldi] bf16, W [experts, N, K] bf16, out [>= rows, ldo] bf16.  With the layout's tables (tile_expert [max_tiles],
+// n_tiles [1], both on the device) tile j of `tile` rows is expert tile_expert[j]'s and rows = max_tiles * tile; without
+// them it is expert 0's product over `rows` rows.  act: 0 none, 1 the square of relu.
+extern "C" int ce_gemm_tc_grouped(const void* x, const void* W, void* out, const int* tile_expert, const int* n_tiles, int max_tiles,
+                                  int tile, int experts, int N, int K, int ldi, int ldo, int x_rows, int rows, int act, int* status,
+                                  cudaStream_t stream) {
+    if (max_tiles == 0 || rows == 0 || N == 0) return CE_OK;
+    if (!x || !W || !out || !status || (tile_expert == nullptr) != (n_tiles == nullptr))
+        return ce_fail(CE_ERR_ARG, "ce_gemm_tc_grouped: null pointer");
+    if (!ce_gemm_tc_grouped_supported(tile, N, K, ldi, ldo) || experts <= 0 || act < 0 || act > 1)
+        return ce_fail(CE_ERR_SIZE, "ce_gemm_tc_grouped: tiles of %d rows, N=%d, K=%d, row stride %d", tile, N, K, ldi);
+    if (((uintptr_t)x | (uintptr_t)W) & 15) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc_grouped: operands must be 16-byte aligned");
+    if (max_tiles > 65535 || (long long)experts * N > 2147483647LL || (long long)max_tiles * tile > (long long)rows + tile - 1 ||
+        x_rows <= 0)
+        return ce_fail(CE_ERR_SIZE, "ce_gemm_tc_grouped: %d tiles of %d rows for %d rows", max_tiles, tile, rows);
+    CUtensorMap mw, mx;
+    int rc = get_map(W, (long long)experts * N, K, K, BM, &mw);
+    if (rc) return rc;
+    if ((rc = get_map(x, x_rows, K, ldi, tile, &mx))) return rc;
+    TcGroupArgs a{(__nv_bfloat16*)out, tile_expert, n_tiles, status, rows, N, K, ldo, (K + BK - 1) / BK, act};
+    dim3 grid((N + BM - 1) / BM, max_tiles);
+    return tile == 64 ? launch_grouped<64>(mw, mx, a, grid, stream) : launch_grouped<128>(mw, mx, a, grid, stream);
 }

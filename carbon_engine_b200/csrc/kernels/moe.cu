@@ -360,6 +360,49 @@ extern "C" int ce_moe_matmul(const void* in, const void* W, void* out, const int
 }
 
 // ---------------------------------------------------------------------------------------------
+// the tokens' rows copied into the layout's order (what a product that loads its rows by TMA reads): row p of the
+// live tiles receives row row_token[p] of the input, zeros where p is padding.  Rows are copied 16 bytes a thread.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* __restrict__ in, long long ldi16, const int* __restrict__ row_token,
+                                                         const int* __restrict__ n_tiles, int BM, uint4* __restrict__ out, int row16,
+                                                         int max_rows) {
+    ce_pdl_begin();
+    const int rows = min(n_tiles[0] * BM, max_rows);
+    const int per = blockDim.x / row16 > 0 ? blockDim.x / row16 : 1;          // rows a block copies at a time
+    for (int p0 = blockIdx.x * per; p0 < rows; p0 += gridDim.x * per) {
+        if (row16 <= (int)blockDim.x) {
+            int p = p0 + threadIdx.x / row16, j = threadIdx.x % row16;
+            if (threadIdx.x < per * row16 && p < rows) {
+                int t = row_token[p];
+                out[(size_t)p * row16 + j] = t >= 0 ? in[(size_t)t * ldi16 + j] : make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            int t = row_token[p0];
+            for (int j = threadIdx.x; j < row16; j += blockDim.x)
+                out[(size_t)p0 * row16 + j] = t >= 0 ? in[(size_t)t * ldi16 + j] : make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// in [T, ldi] -> out [max_rows, K] (contiguous), elements of `elsize` bytes; K * elsize and ldi * elsize multiples of 16
+extern "C" int ce_moe_gather(const void* in, int ldi, int K, int elsize, const int* row_token, const int* n_tiles, int BM, void* out,
+                             int max_rows, cudaStream_t stream) {
+    if (max_rows == 0 || K == 0) return CE_OK;
+    if (!in || !row_token || !n_tiles || !out) return ce_fail(CE_ERR_ARG, "ce_moe_gather: null pointer");
+    if (((long long)K * elsize) % 16 || ((long long)ldi * elsize) % 16 || (((uintptr_t)in | (uintptr_t)out) & 15) || BM <= 0)
+        return ce_fail(CE_ERR_SIZE, "ce_moe_gather: rows of %d elements of %d bytes are not whole 16-byte pieces", K, elsize);
+    int row16 = (int)((long long)K * elsize / 16);
+    int per = 256 / row16 > 0 ? 256 / row16 : 1;
+    int blocks = (max_rows + per - 1) / per;
+    int cap = ce_sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    ce_note("moe_gather_kernel");
+    ce_launch(moe_gather_kernel, blocks, 256, 0, stream, (const uint4*)in, (long long)ldi * elsize / 16, row_token, n_tiles, BM, (uint4*)out,
+              row16, max_rows);
+    return ce_check_launch("ce_moe_gather");
+}
+
+// ---------------------------------------------------------------------------------------------
 // back to token order
 // ---------------------------------------------------------------------------------------------
 template <typename T>

@@ -705,6 +705,16 @@ def moe_matmul(inp: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile: int,
                                 rows, _stream()))
 
 
+def moe_gather(inp: torch.Tensor, row_token: torch.Tensor, n_tiles: torch.Tensor, tile: int, out: torch.Tensor) -> None:
+    """out[p] = inp[row_token[p]] (zeros where row_token[p] < 0) for the rows of the layout's live tiles; rows of whole
+    16-byte pieces."""
+    _need(out, "out", inp.dtype); _need(row_token, "row_token", torch.int32); _need(n_tiles, "n_tiles", torch.int32)
+    if inp.stride(-1) != 1 or out.shape[1] != inp.shape[1] or row_token.numel() < out.shape[0]:
+        raise KernelError("moe_gather: shapes do not fit")
+    _ok(kernels().ce_moe_gather(_ptr(inp), inp.stride(0), inp.shape[1], inp.element_size(), _ptr(row_token), _ptr(n_tiles), int(tile),
+                                _ptr(out), out.shape[0], _stream()))
+
+
 def moe_combine(rows: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, y: torch.Tensor, shared=None, sgate=None,
                 accumulate: bool = False) -> None:
     """y[t] (+)= sum_k weights[t, k] * rows[pair_row[t * top + k]] (+ sgate[t] * shared[t]); y float32 [T, W]."""

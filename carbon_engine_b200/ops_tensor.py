@@ -26,6 +26,9 @@ kernel_lib.declare("ce_gemm_tc_scratch", _ll, [_i, _i, _i, _i])
 kernel_lib.declare("ce_gemm_tc_splits", _i, [_i, _i, _i])
 # A, W, C, M, N, K, lda, ldc, mode, scratch, scratch_floats, counters, n_counters, status, stream
 kernel_lib.declare("ce_gemm_tc", _i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _i, _p, _p])
+kernel_lib.declare("ce_gemm_tc_grouped_supported", _i, [_i, _i, _i, _i, _i])
+# x, W, out, tile_expert, n_tiles, max_tiles, tile, experts, N, K, ldi, ldo, x_rows, rows, act, status, stream
+kernel_lib.declare("ce_gemm_tc_grouped", _i, [_p] * 5 + [_i] * 10 + [_p, _p])
 
 
 def decode_split() -> int:
@@ -99,6 +102,40 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) ->
     ops._ok(k.ce_gemm_tc(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), out.stride(0), mode,
                          ws.scratch.data_ptr(), ws.scratch.numel(), ws.counters.data_ptr(), ws.counters.numel(),
                          ws.status.data_ptr(), ops._stream()))
+    return True
+
+
+def grouped_bf16_supported(tile: int, n: int, k: int, ldi: int, ldo: int, dtype) -> bool:
+    """Whether :func:`grouped_bf16` takes tiles of ``tile`` rows and products of these sizes."""
+    return USE_TENSOR_GEMM and dtype == torch.bfloat16 and bool(kernels().ce_gemm_tc_grouped_supported(tile, n, k, ldi, ldo))
+
+
+def grouped_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile: int, act: int, tile_expert=None, n_tiles=None) -> bool:
+    """out[p] = act(x[p] @ w[tile_expert[p // tile]].T) over a layout by expert on the tcgen05 kernel (w [experts, N, K]; x
+    already in the layout's order), or, without the tables, out = act(x @ w[0].T); False if the shape is refused."""
+    if x.dim() != 2 or x.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous() or w.dtype != x.dtype or out.dtype != x.dtype:
+        return False
+    E, N, K = w.shape
+    if not grouped_bf16_supported(tile, N, K, x.stride(0), out.stride(0), x.dtype) or (x.data_ptr() | w.data_ptr()) & 15:
+        return False
+    if tile_expert is None:
+        rows = x.shape[0]
+        tiles = (rows + tile - 1) // tile
+        if out.shape[0] < rows:
+            return False
+    else:
+        tiles = tile_expert.numel()
+        rows = tiles * tile
+        if out.shape[0] < rows or x.shape[0] < rows:
+            return False
+    prof = ops.profiling()
+    if prof is not None:
+        live = min(E, max(tiles, 1))
+        prof.note_work((rows * (N + K) + live * N * K) * 2, 2 * rows * N * K)
+    ws = gemm_workspace(x.device)
+    ops._ok(kernels().ce_gemm_tc_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._ptr(tile_expert), ops._ptr(n_tiles), tiles,
+                                         tile, E, N, K, x.stride(0), out.stride(0), x.shape[0], rows, act, ws.status.data_ptr(),
+                                         ops._stream()))
     return True
 
 

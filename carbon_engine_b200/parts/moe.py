@@ -11,6 +11,9 @@ The experts' matrices are held as two stacks [experts, ff, hidden] and [experts,
 pairs are laid out by expert on the device (every expert's rows start a tile), the two products run as grouped products
 over that layout, and a last kernel sums each token's rows in the order of its picks.  Nothing of the routing reaches
 the host, so a step of a given size launches the same grids whatever the router says (a decode step can be captured).
+Steps of many tokens in bfloat16 take tiles of 64 or 128 rows on the tcgen05 product (``gemm_tc.cu``'s grouped kernel, which
+loads its rows by TMA: the tokens' rows are first copied into the layout's order); steps of single tokens take tiles of 16
+rows on the kernels of ``moe.cu``, which read the tokens' rows where they lie.
 The router's product also yields the shared expert's gate logit (its row is appended to the router's).
 """
 from __future__ import annotations
@@ -19,7 +22,7 @@ from typing import List, Optional
 
 import torch
 
-from .. import ops
+from .. import ops, ops_tensor
 from .base import FeedForward, Part, TensorGetter, TensorSpec, to_device
 from .linear import STORE_F32, Linear
 
@@ -74,14 +77,29 @@ class RoutedExperts(FeedForward):
             self.shared_up = to_device(get(f"{p}.shared.up"), device, dtype).unsqueeze(0)
             self.shared_down = to_device(get(f"{p}.shared.down"), device, dtype).unsqueeze(0)
 
-    def tile_for(self, tokens: int) -> int:
-        return 16 if tokens * self.top <= self.SMALL_TILE_MAX * self.experts else 64
+    def tile_for(self, tokens: int, dtype=None) -> int:
+        """Rows of a tile of the layout: 16 for steps of single tokens; else 64, or 128 where the tensor-core product takes
+        the sizes and the experts have rows enough to fill such tiles."""
+        pairs = tokens * self.top
+        if pairs <= self.SMALL_TILE_MAX * self.experts:
+            return 16
+        if pairs >= 128 * self.experts and self._fast(128, dtype):
+            return 128
+        return 64
+
+    def _fast(self, tile: int, dtype) -> bool:
+        return tile >= 64 and ops_tensor.grouped_bf16_supported(tile, self.ff, self.hidden, self.hidden, self.ff, dtype) and \
+            ops_tensor.grouped_bf16_supported(tile, self.hidden, self.ff, self.ff, self.hidden, dtype)
 
     def step_bytes(self, tokens: int, element_size: int) -> int:
-        tile = self.tile_for(tokens)
-        rows = ops.moe_max_tiles(tokens * self.top, self.experts, tile) * tile
-        return rows * (self.ff + self.hidden) * element_size + tokens * (self.shared_ff + self.hidden) * element_size \
+        rows = max(ops.moe_max_tiles(tokens * self.top, self.experts, tile) * tile for tile in (16, 64, 128))
+        return rows * (self.ff + 2 * self.hidden) * element_size + tokens * (self.shared_ff + self.hidden) * element_size \
             + tokens * (self.router.padded_out + 3 * self.top + 1) * 4 + rows * 4
+
+    def _product(self, x, w, out, tile, activation, fast, row_token=None, tile_expert=None, n_tiles=None) -> None:
+        if fast and row_token is None and ops_tensor.grouped_bf16(x, w, out, tile, ops.MOE_ACTIVATIONS[activation], tile_expert, n_tiles):
+            return
+        ops.moe_matmul(x, w, out, tile, activation, row_token, tile_expert, n_tiles)
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
         T, E, top = h.shape[0], self.experts, self.top
@@ -91,19 +109,29 @@ class RoutedExperts(FeedForward):
         ids, weights = ctx.buffer((T, top), torch.int32), ctx.buffer((T, top), torch.float32)
         sgate = ctx.buffer((T,), torch.float32) if self.shared_gate else None
         ops.moe_route(z, E, top, self.groups, self.keep_groups, self.scale, ids, weights, sgate)
-        tile = self.tile_for(T)
+        tile = self.tile_for(T, h.dtype)
+        fast = self._fast(tile, h.dtype)
         tiles = ops.moe_max_tiles(T * top, E, tile)
         row_token, pair_row, tile_expert, n_tiles = i32(tiles * tile), i32(T * top), i32(tiles), i32(1)
         ops.moe_align(ids, E, tile, row_token, pair_row, tile_expert, n_tiles)
         act = ctx.buffer((tiles * tile, self.ff))
-        ops.moe_matmul(h, self.up, act, tile, self.activation, row_token, tile_expert, n_tiles)
+        if fast:
+            laid = ctx.buffer((tiles * tile, self.hidden))
+            ops.moe_gather(h, row_token, n_tiles, tile, laid)
+            self._product(laid, self.up, act, tile, self.activation, True, None, tile_expert, n_tiles)
+        else:
+            ops.moe_matmul(h, self.up, act, tile, self.activation, row_token, tile_expert, n_tiles)
         rows = ctx.buffer((tiles * tile, self.hidden))
-        ops.moe_matmul(act, self.down, rows, tile, "none", None, tile_expert, n_tiles)
+        self._product(act, self.down, rows, tile, "none", fast, None, tile_expert, n_tiles)
         shared = None
         if self.shared_ff > 0:
-            st = 16 if T <= 16 else 64
+            st = 16 if T <= 16 else 64 if T < 1024 else 128
+            sfast = st >= 64 and ops_tensor.grouped_bf16_supported(st, self.shared_ff, self.hidden, self.hidden, self.shared_ff, h.dtype) \
+                and ops_tensor.grouped_bf16_supported(st, self.hidden, self.shared_ff, self.shared_ff, self.hidden, h.dtype)
+            if not sfast:
+                st = min(st, 64)
             sact = ctx.buffer((T, self.shared_ff))
-            ops.moe_matmul(h, self.shared_up, sact, st, self.activation)
+            self._product(h, self.shared_up, sact, st, self.activation, sfast)
             shared = ctx.buffer((T, self.hidden))
-            ops.moe_matmul(sact, self.shared_down, shared, st, "none")
+            self._product(sact, self.shared_down, shared, st, "none", sfast)
         ops.moe_combine(rows, pair_row, weights, x, shared, sgate, accumulate)

@@ -165,27 +165,39 @@ def small_expert(w: Dict[str, torch.Tensor], p: str, h: torch.Tensor) -> torch.T
     return relu_squared(h @ w[f"{p}.up"].T) @ w[f"{p}.down"].T
 
 
-def route(z: torch.Tensor, router: dict) -> Tuple[List[int], List[float]]:
-    """One token's router logits -> the chosen experts and their weights."""
+def route(z: torch.Tensor, router: dict, margin: Optional[list] = None) -> Tuple[List[int], List[float]]:
+    """One token's router logits -> the chosen experts and their weights.  ``margin`` receives how clear the choice was:
+    the smallest gap between something chosen and something not (the last kept group and the first dropped one; the last
+    chosen expert and the first one passed over), in logits, as a fraction of the logits' spread."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.softmax(z, dim=-1)
     allowed = list(range(E))
     groups = router.get("groups")
+    gap = math.inf
     if groups:
-        n, size = int(groups["count"]), E // int(groups["count"])
-        best = sorted(range(n), key=lambda g: -float(s[g * size:(g + 1) * size].max()))[:int(groups["keep"])]
+        n, size, keep = int(groups["count"]), E // int(groups["count"]), int(groups["keep"])
+        order = sorted(range(n), key=lambda g: -float(s[g * size:(g + 1) * size].max()))
+        best = order[:keep]
         allowed = [e for e in range(E) if e // size in best]
-    chosen = sorted(allowed, key=lambda e: -float(s[e]))[:top]
+        if keep < n:
+            gap = float(z[order[keep - 1] * size:(order[keep - 1] + 1) * size].max() - z[order[keep] * size:(order[keep] + 1) * size].max())
+    ranked = sorted(allowed, key=lambda e: -float(s[e]))
+    chosen = ranked[:top]
+    if top < len(ranked):
+        gap = min(gap, float(z[ranked[top - 1]] - z[ranked[top]]))
+    if margin is not None:
+        margin.append(gap / max(float(z.max() - z.min()), 1e-30))
     total = sum(float(s[e]) for e in chosen) + 1e-20
     scale = float(router.get("scale", 1.0))
     return chosen, [float(s[e]) / total * scale for e in chosen]
 
 
-def moe_ffn(w: Dict[str, torch.Tensor], p: str, mlp: dict, h: torch.Tensor) -> torch.Tensor:
+def moe_ffn(w: Dict[str, torch.Tensor], p: str, mlp: dict, h: torch.Tensor, margins: Optional[list] = None) -> torch.Tensor:
+    """``margins`` receives one number per token: see :func:`route`."""
     out = torch.zeros_like(h)
     z = h @ w[f"{p}.router"].T
     for t in range(h.shape[0]):
-        chosen, weights = route(z[t], mlp["router"])
+        chosen, weights = route(z[t], mlp["router"], margins)
         for e, g in zip(chosen, weights):
             out[t] += g * small_expert(w, f"{p}.e{e}", h[t:t + 1])[0]
     if mlp.get("shared"):
@@ -197,9 +209,10 @@ def moe_ffn(w: Dict[str, torch.Tensor], p: str, mlp: dict, h: torch.Tensor) -> t
 # the model
 # ---------------------------------------------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], tap: Optional[Callable] = None,
-            round_input: Optional[Callable] = None) -> torch.Tensor:
+            round_input: Optional[Callable] = None, margins: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence from its first token.  ``tap(i, x)`` sees the residual after layer i.
-    ``round_input``: applied to what the sublayers read (to see what a rounding of the activations does)."""
+    ``round_input``: applied to what the sublayers read (to see what a rounding of the activations does).
+    ``margins`` receives, per mixture layer, a list with every token's router margin (:func:`route`)."""
     eps = float(cfg["norm"]["eps"])
     rd = round_input or (lambda t: t)
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)].to(F)
@@ -213,7 +226,13 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], tap: Optio
         x = x + norm_zero_centred(y, w[f"{p}.norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = dense_ffn(w, f"{p}.mlp", rd(x)) if mlp["kind"] == "dense" else moe_ffn(w, f"{p}.mlp", mlp, rd(x))
+            if mlp["kind"] == "dense":
+                y = dense_ffn(w, f"{p}.mlp", rd(x))
+            else:
+                per_token: list = []
+                y = moe_ffn(w, f"{p}.mlp", mlp, rd(x), per_token)
+                if margins is not None:
+                    margins.append(per_token)
             x = x + norm_zero_centred(y, w[f"{p}.norm2"], eps)
         if tap is not None:
             tap(i, x)

@@ -64,11 +64,11 @@ CASES: Dict[str, dict] = {
     "T": config([layer(heads=8, dim=16, rot_dim=16, vdim=32, kv_rank=48, scale=0.18, rotation=rot(dims=16, base=1e4, factor=4.0, original=64, fast=16.0), mlp=dense(96)),
                  layer(heads=8, dim=32, rot_dim=16, vdim=16, kv_rank=48, scale=0.15, rotation=rot(dims=16, base=1e4, factor=4.0, original=64, fast=16.0), kv_from=0,
                        mlp=moe(experts=8, top=2, ff=32, groups=(4, 2), scale=2.0, shared=48))], width=64, vocab=151),
-    # a mid-sized model's head sizes: latent rows of 128 + 32
-    "V": config([layer(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=128, scale=0.125, rotation=rot(dims=32, base=5e5, factor=2.0, original=96, fast=32.0),
-                       mlp=moe(experts=16, top=4, ff=64, groups=(4, 2), scale=2.5, shared=128)),
-                 layer(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=128, scale=0.125, rotation=rot(dims=32, base=5e5, factor=2.0, original=96, fast=32.0), kv_from=0,
-                       mlp=dense(384))], width=256, vocab=300),
+    # wider heads and a latent wider than a head: rows of 192 + 32, values cut into slices by the tensor-core kernel
+    "V": config([layer(heads=4, dim=64, rot_dim=32, vdim=64, kv_rank=192, scale=0.1, rotation=rot(dims=32, base=1e4, factor=4.0, original=128, fast=16.0),
+                       mlp=moe(experts=16, top=4, ff=48, groups=(4, 2), scale=2.0, shared=96)),
+                 layer(heads=4, dim=64, rot_dim=32, vdim=64, kv_rank=192, scale=0.1, rotation=rot(dims=32, base=1e4, factor=4.0, original=128, fast=16.0), kv_from=0,
+                       mlp=dense(272))], width=192, vocab=300),
 }
 #: one layer alone, for looking at a mechanism by itself
 SINGLE = {
