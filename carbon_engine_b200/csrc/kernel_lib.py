@@ -32,10 +32,12 @@ _SIGNATURES = {
     "ce_add_residual": (_i, [_p, _p, _i, _ll, _p]),
     "ce_swiglu": (_i, [_p, _p, _i, _i, _i, _p]),
     "ce_reluglu": (_i, [_p, _p, _i, _i, _i, _p]),
+    # in, out, dtype, T, I, ldo, stream
+    "ce_relu2": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     # x, w, b, out, out_dtype, rows, R, H, eps, stream
     "ce_layernorm": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
     # y, w, x, T, H, eps, stream
-    "ce_rmsnorm_add": (_i, [_p, _p, _p, _i, _i, _f, _p]),
+    "ce_rmsnorm_add": (_i, [_p, _p, _p, _p, _i, _i, _f, _p]),
     # x, n, cap, stream
     "ce_tanh_cap": (_i, [_p, _ll, _f, _p]),
     # src, out, out_dtype, T, ld, off, L, stream

@@ -512,6 +512,30 @@ extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cud
     return gated_act(gu, out, dtype, T, I, 0, stream);
 }
 
+// out[t, i] = relu(in[t, i])^2: the epilogue of a library product for the activation of the small experts
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, int I, int ldo, size_t total) {
+    ce_pdl_begin();
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        size_t t = i / I, c = i - t * I;
+        float v = fmaxf(CeType<T>::load(in + i), 0.f);
+        CeType<T>::store(out + t * ldo + c, v * v);
+    }
+}
+
+extern "C" int ce_relu2(const void* in, void* out, int dtype, int T, int I, int ldo, cudaStream_t stream) {
+    size_t total = (size_t)T * I;
+    if (total == 0) return CE_OK;
+    if (!in || !out) return ce_fail(CE_ERR_ARG, "ce_relu2: null pointer");
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    ce_note("relu2_kernel");
+    if (dtype == CE_F32) ce_launch(relu2_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, I, ldo, total);
+    else if (dtype == CE_BF16) ce_launch(relu2_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, ldo, total);
+    else return ce_fail(CE_ERR_ARG, "ce_relu2: unknown dtype %d", dtype);
+    return ce_check_launch("ce_relu2");
+}
+
 // ---------------------------------------------------------------------------------------------
 // dst[idx[i]] = val[i]: applies the block-table entries that changed since the last step.
 // ---------------------------------------------------------------------------------------------

@@ -15,7 +15,7 @@
 #define GP_BN 64
 #define GP_BK 16
 
-enum { GP_STORE = 0, GP_STORE_F32 = 1, GP_ACCUM_F32 = 2, GP_SWIGLU = 3, GP_RELUGLU = 4 };     // 4: relu(gate) * up
+enum { GP_STORE = 0, GP_STORE_F32 = 1, GP_ACCUM_F32 = 2, GP_SWIGLU = 3, GP_RELUGLU = 4, GP_RELU2 = 5 };     // 4: relu(gate) * up; 5: relu(v)^2
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(const T* __restrict__ A, const T* __restrict__ W,
@@ -79,6 +79,9 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(const T* __restrict__ A
                 ((float*)Cv)[o] = acc[0][i][j];
             } else if (MODE == GP_ACCUM_F32) {
                 ((float*)Cv)[o] += acc[0][i][j];
+            } else if (MODE == GP_RELU2) {
+                float v = fmaxf(acc[0][i][j], 0.f);
+                CeType<T>::store((T*)Cv + o, v * v);
             } else if (MODE == GP_RELUGLU) {
                 CeType<T>::store((T*)Cv + o, fmaxf(acc[0][i][j], 0.f) * acc[NW - 1][i][j]);
             } else {
@@ -99,6 +102,7 @@ static int launch_plain(const void* A, const void* W, void* C, int M, int N, int
         case GP_ACCUM_F32: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_ACCUM_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         case GP_SWIGLU: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_SWIGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         case GP_RELUGLU: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_RELUGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
+        case GP_RELU2: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_RELU2>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         default: return ce_fail(CE_ERR_ARG, "ce_gemm_plain: unknown epilogue %d", mode);
     }
     return ce_check_launch("ce_gemm_plain");

@@ -38,7 +38,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;     // with the back-off below: about a second at most
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ACCUM_F32 = 2, TC_SWIGLU = 3, TC_RELUGLU = 4 };     // 4: relu(gate) * up, laid out and tiled like 3
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ACCUM_F32 = 2, TC_SWIGLU = 3, TC_RELUGLU = 4, TC_RELU2 = 5 };     // 4: relu(gate) * up, laid out and tiled like 3; 5: relu(v)^2 stored like 0
 #define TC_GATED(mode) ((mode) == TC_SWIGLU || (mode) == TC_RELUGLU)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -149,6 +149,7 @@ __device__ __forceinline__ void epilogue_store(const TcArgs& a, int m, int n, fl
     if (a.mode == TC_STORE) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
     else if (a.mode == TC_STORE_F32) ((float*)a.out)[o] = v;
     else if (a.mode == TC_ACCUM_F32) ((float*)a.out)[o] += v;
+    else if (a.mode == TC_RELU2) { float r = fmaxf(v, 0.f); ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(r * r); }
     else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(gated_mul(a.mode, v, up));
 }
 
@@ -1310,7 +1311,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     if (!ce_gemm_tc_supported(M, N, K, lda))
         return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: K=%d and the row stride %d must be multiples of 8", K, lda);
     if (((uintptr_t)A | (uintptr_t)W) & 15) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: operands must be 16-byte aligned");
-    if (mode < 0 || mode > 4) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
+    if (mode < 0 || mode > 5) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
     int nacc = TC_GATED(mode) ? 2 : 1;
     int kblocks = (K + BK - 1) / BK;
     bool early_pairs = pairs_from_129(M, N, nacc);
@@ -1413,7 +1414,7 @@ int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, const TcGroupAr
 }  // namespace
 
 extern "C" int ce_gemm_tc_grouped_supported(int tile, int N, int K, int ldi, int ldo) {
-    return (tile == 64 || tile == 128) && N > 0 && K > 0 && K % 8 == 0 && ldi % 8 == 0 && ldo > 0;
+    return (tile == 16 || tile == 32 || tile == 64 || tile == 128) && N > 0 && K > 0 && K % 8 == 0 && ldi % 8 == 0 && ldo > 0;
 }
 
 // x [x_rows, ldi] bf16, W [experts, N, K] bf16, out [>= rows, ldo] bf16.  With the layout's tables (tile_expert [max_tiles],
@@ -1437,5 +1438,10 @@ extern "C" int ce_gemm_tc_grouped(const void* x, const void* W, void* out, const
     if ((rc = get_map(x, x_rows, K, ldi, tile, &mx))) return rc;
     TcGroupArgs a{(__nv_bfloat16*)out, tile_expert, n_tiles, status, rows, N, K, ldo, (K + BK - 1) / BK, act};
     dim3 grid((N + BM - 1) / BM, max_tiles);
-    return tile == 64 ? launch_grouped<64>(mw, mx, a, grid, stream) : launch_grouped<128>(mw, mx, a, grid, stream);
+    switch (tile) {
+        case 16: return launch_grouped<16>(mw, mx, a, grid, stream);
+        case 32: return launch_grouped<32>(mw, mx, a, grid, stream);
+        case 64: return launch_grouped<64>(mw, mx, a, grid, stream);
+        default: return launch_grouped<128>(mw, mx, a, grid, stream);
+    }
 }

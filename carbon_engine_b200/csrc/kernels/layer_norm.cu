@@ -109,7 +109,8 @@ extern "C" int ce_layernorm(const float* x, const float* w, const float* b, void
 // ---------------------------------------------------------------------------------------------
 // x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w      (y float32, x the float32 residual stream)
 // ---------------------------------------------------------------------------------------------
-__global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x, int H, float eps) {
+__global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x,
+                                   __nv_bfloat16* __restrict__ xb, int H, float eps) {
     ce_pdl_begin();
     __shared__ float scratch[32];
     int t = blockIdx.x;
@@ -117,11 +118,16 @@ __global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __r
     float q = 0.f;
     for (int j = threadIdx.x; j < H; j += blockDim.x) q = fmaf(yr[j], yr[j], q);
     float inv = 1.0f / sqrtf(ce_block_sum(q, scratch) / (float)H + eps);
-    for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] += yr[j] * inv * w[j];
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = x[(size_t)t * H + j] + yr[j] * inv * w[j];
+        x[(size_t)t * H + j] = v;
+        if (xb) xb[(size_t)t * H + j] = __float2bfloat16_rn(v);
+    }
 }
 
 // The same with float4 loads, y kept in registers between the two passes (widths in multiples of 4 up to 4 * threads * LNV_MAX)
-__global__ void rmsnorm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x, int H, float eps) {
+__global__ void rmsnorm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x,
+                                       __nv_bfloat16* __restrict__ xb, int H, float eps) {
     ce_pdl_begin();
     __shared__ float scratch[32];
     int t = blockIdx.x, H4 = H >> 2;
@@ -144,23 +150,29 @@ __global__ void rmsnorm_add_vec_kernel(const float* __restrict__ y, const float*
             float4 xv = xr[j], ww = w4[j];
             xv.x += v[n].x * inv * ww.x; xv.y += v[n].y * inv * ww.y; xv.z += v[n].z * inv * ww.z; xv.w += v[n].w * inv * ww.w;
             xr[j] = xv;
+            if (xb) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(xv.x, xv.y), hi = __floats2bfloat162_rn(xv.z, xv.w);
+                uint2 packed = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+                reinterpret_cast<uint2*>(xb + (size_t)t * H)[j] = packed;
+            }
         }
     }
 }
 
-extern "C" int ce_rmsnorm_add(const float* y, const float* w, float* x, int T, int H, float eps, cudaStream_t stream) {
+// xb (or null): receives the new x rounded to bfloat16, what a sublayer that reads the residual itself takes as its input
+extern "C" int ce_rmsnorm_add(const float* y, const float* w, float* x, void* xb, int T, int H, float eps, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!y || !w || !x) return ce_fail(CE_ERR_ARG, "ce_rmsnorm_add: null pointer");
-    if (H % 4 == 0 && H >= 256 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0)) {
+    if (H % 4 == 0 && H >= 256 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) && (((uintptr_t)xb) & 7) == 0) {
         int H4 = H / 4, vt = H4 >= 2048 ? 1024 : H4 >= 512 ? 512 : H4 >= 256 ? 256 : 128;
         if (H4 <= vt * LNV_MAX) {
             ce_note("rmsnorm_add_vec_kernel");
-            ce_launch(rmsnorm_add_vec_kernel, T, vt, 0, stream, y, w, x, H, eps);
+            ce_launch(rmsnorm_add_vec_kernel, T, vt, 0, stream, y, w, x, (__nv_bfloat16*)xb, H, eps);
             return ce_check_launch("ce_rmsnorm_add");
         }
     }
     ce_note("rmsnorm_add_kernel");
-    ce_launch(rmsnorm_add_kernel, T, H >= 4096 ? 512 : H >= 1024 ? 256 : 128, 0, stream, y, w, x, H, eps);
+    ce_launch(rmsnorm_add_kernel, T, H >= 4096 ? 512 : H >= 1024 ? 256 : 128, 0, stream, y, w, x, (__nv_bfloat16*)xb, H, eps);
     return ce_check_launch("ce_rmsnorm_add");
 }
 

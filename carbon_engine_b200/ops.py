@@ -14,7 +14,7 @@ import torch
 from .csrc.kernel_lib import KernelError, kernels
 
 F32, BF16 = 0, 1
-GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU, GEMM_RELUGLU = 0, 1, 2, 3, 4
+GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU, GEMM_RELUGLU, GEMM_RELU2 = 0, 1, 2, 3, 4, 5      # 5: relu(v)^2, stored like 0
 #: epilogues whose weight holds gate rows and up rows: act(gate) * up with act = SiLU or ReLU
 GEMM_GATED = (GEMM_SWIGLU, GEMM_RELUGLU)
 ROPE_PAIRINGS = {"half": 0, "interleaved": 1}
@@ -253,6 +253,14 @@ def reluglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _ok(kernels().ce_reluglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()))
 
 
+def relu2(inp: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = relu(inp[t, i])^2; inp contiguous [T, I], out rows of stride out.stride(0)."""
+    _need(inp, "inp")
+    if out.dtype != inp.dtype or out.shape != inp.shape or out.stride(-1) != 1 or not out.is_cuda:
+        raise KernelError("relu2: shapes or dtypes do not fit")
+    _ok(kernels().ce_relu2(_ptr(inp), _ptr(out), dtype_code(out.dtype), inp.shape[0], inp.shape[1], out.stride(0), _stream()))
+
+
 def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, eps: float,
               rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = (x - mean) / sqrt(var + eps) * weight + bias of row rows[r] (or r); x float32."""
@@ -266,12 +274,17 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: to
                                _stream()))
 
 
-def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float) -> None:
-    """x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight; all float32."""
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float, rounded: Optional[torch.Tensor] = None) -> None:
+    """x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight; all float32.  ``rounded`` (bfloat16, the shape of x, contiguous)
+    receives the new x rounded: the input of a sublayer that reads the residual itself."""
     _need(y, "y", torch.float32); _need(weight, "weight", torch.float32); _need(x, "x", torch.float32)
     if y.shape != x.shape or weight.numel() != x.shape[1]:
         raise KernelError("rmsnorm_add: sizes differ")
-    _ok(kernels().ce_rmsnorm_add(_ptr(y), _ptr(weight), _ptr(x), x.shape[0], x.shape[1], float(eps), _stream()))
+    if rounded is not None:
+        _need(rounded, "rounded", torch.bfloat16)
+        if rounded.shape != x.shape:
+            raise KernelError("rmsnorm_add: the rounded copy must have the shape of x")
+    _ok(kernels().ce_rmsnorm_add(_ptr(y), _ptr(weight), _ptr(x), _ptr(rounded), x.shape[0], x.shape[1], float(eps), _stream()))
 
 
 def tanh_cap(x: torch.Tensor, cap: float) -> None:

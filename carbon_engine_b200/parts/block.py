@@ -62,25 +62,41 @@ class OutputNormBlock(Block):
         ffn = self.ffn.step_bytes(tokens, element_size) if self.ffn is not None else 0
         return tokens * self.width * (element_size + 4) + max(self.mixer.step_bytes(tokens, element_size), ffn)
 
+    #: what the norm before left in ``ctx.shared``: the residual rounded to bfloat16, and whose rounding it is
+    ROUNDED = "residual.rounded"
+
     def _read(self, ctx, x: torch.Tensor) -> torch.Tensor:
         if ctx.dtype == torch.float32:
             return x
+        left = ctx.shared.pop(self.ROUNDED, None)
+        if left is not None and left[1] == x.data_ptr() and left[0].shape == x.shape:
+            return left[0]
         h = ctx.buffer(tuple(x.shape))
         ops.copy_cols(x, 0, x.shape[1], h)
         return h
+
+    def _add(self, ctx, norm: Norm, y: torch.Tensor, x: torch.Tensor) -> None:
+        """x += norm(y); in bfloat16 the norm's kernel also leaves the new residual rounded for the sublayer that reads it
+        next (this block's feed-forward, or the next block's mixer)."""
+        if ctx.dtype != torch.bfloat16:
+            norm.add_into(y, x)
+            return
+        h = ctx.buffer(tuple(x.shape))
+        norm.add_into(y, x, rounded=h)
+        ctx.shared[self.ROUNDED] = (h, x.data_ptr())
 
     def forward(self, ctx, x: torch.Tensor, cache) -> None:
         y = ctx.buffer(tuple(x.shape), torch.float32)
         owed = self.mixer.forward(ctx, self._read(ctx, x), y, cache, accumulate=False)
         if owed is not None:
             ops.add_bias(y, owed)
-        self.mixer_norm.add_into(y, x)
+        self._add(ctx, self.mixer_norm, y, x)
         if self.ffn is None:
             return
         owed = self.ffn.forward(ctx, self._read(ctx, x), y, accumulate=False)
         if owed is not None:
             ops.add_bias(y, owed)
-        self.ffn_norm.add_into(y, x)
+        self._add(ctx, self.ffn_norm, y, x)
 
 
 class StreamBlock(Block):

@@ -20,6 +20,7 @@ from .. import ops
 from .base import Part, TensorGetter, TensorSpec, to_device
 
 STORE, STORE_F32, ACCUM, SWIGLU, RELUGLU = ops.GEMM_STORE, ops.GEMM_STORE_F32, ops.GEMM_ACCUM_F32, ops.GEMM_SWIGLU, ops.GEMM_RELUGLU
+RELU2 = ops.GEMM_RELU2
 
 #: bfloat16 products go to "tensor" (own tcgen05 kernels), "library" (cuBLAS + epilogue kernel) or
 #: "plain" (the FMA kernel); "auto" takes the first that accepts the shape.
@@ -61,6 +62,8 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, sc
         ops.swiglu(torch.matmul(a, w.t()), out)
     elif mode == RELUGLU:
         ops.reluglu(torch.matmul(a, w.t()), out)
+    elif mode == RELU2:
+        ops.relu2(torch.matmul(a, w.t()), out)
     else:
         raise ValueError(f"unknown epilogue {mode}")
 

@@ -11,9 +11,10 @@ The experts' matrices are held as two stacks [experts, ff, hidden] and [experts,
 pairs are laid out by expert on the device (every expert's rows start a tile), the two products run as grouped products
 over that layout, and a last kernel sums each token's rows in the order of its picks.  Nothing of the routing reaches
 the host, so a step of a given size launches the same grids whatever the router says (a decode step can be captured).
-Steps of many tokens in bfloat16 take tiles of 64 or 128 rows on the tcgen05 product (``gemm_tc.cu``'s grouped kernel, which
-loads its rows by TMA: the tokens' rows are first copied into the layout's order); steps of single tokens take tiles of 16
-rows on the kernels of ``moe.cu``, which read the tokens' rows where they lie.
+In bfloat16, with sizes the kernel takes, the products run on the tcgen05 grouped kernel of ``gemm_tc.cu`` (tiles of 16 rows
+in steps of single tokens, of 64 or 128 rows in steps of many); it loads its rows by TMA, so the tokens' rows are first
+copied into the layout's order.  Other sizes and float32 take the kernels of ``moe.cu``, which read the tokens' rows where
+they lie.  The shared expert is two ordinary products.
 The router's product also yields the shared expert's gate logit (its row is appended to the router's).
 """
 from __future__ import annotations
@@ -24,7 +25,7 @@ import torch
 
 from .. import ops, ops_tensor
 from .base import FeedForward, Part, TensorGetter, TensorSpec, to_device
-from .linear import STORE_F32, Linear
+from .linear import RELU2, STORE, STORE_F32, Linear
 
 
 class RoutedExperts(FeedForward):
@@ -51,19 +52,18 @@ class RoutedExperts(FeedForward):
         self.router = Linear(hidden, sizes, names, pad_rows_to=4)
         self.up: Optional[torch.Tensor] = None            # [experts, ff, hidden]
         self.down: Optional[torch.Tensor] = None          # [experts, hidden, ff]
-        self.shared_up: Optional[torch.Tensor] = None     # [1, shared_ff, hidden]
-        self.shared_down: Optional[torch.Tensor] = None   # [1, hidden, shared_ff]
+        # the shared expert is two ordinary products (the activation is the first one's epilogue)
+        self.shared_up = Linear(hidden, [self.shared_ff], [f"{prefix}.shared.up"]) if self.shared_ff > 0 else None
+        self.shared_down = Linear(self.shared_ff, [hidden], [f"{prefix}.shared.down"]) if self.shared_ff > 0 else None
 
     def children(self) -> List[Part]:
-        return [self.router]
+        return [c for c in (self.router, self.shared_up, self.shared_down) if c is not None]
 
     def tensor_specs(self) -> List[TensorSpec]:
         p = self.prefix
         specs = []
         for e in range(self.experts):
             specs += [TensorSpec(f"{p}.e{e}.up", (self.ff, self.hidden)), TensorSpec(f"{p}.e{e}.down", (self.hidden, self.ff))]
-        if self.shared_ff > 0:
-            specs += [TensorSpec(f"{p}.shared.up", (self.shared_ff, self.hidden)), TensorSpec(f"{p}.shared.down", (self.hidden, self.shared_ff))]
         return specs
 
     def load(self, get: TensorGetter, device, dtype) -> None:
@@ -73,9 +73,6 @@ class RoutedExperts(FeedForward):
         for e in range(self.experts):
             self.up[e].copy_(to_device(get(f"{p}.e{e}.up"), device, dtype))
             self.down[e].copy_(to_device(get(f"{p}.e{e}.down"), device, dtype))
-        if self.shared_ff > 0:
-            self.shared_up = to_device(get(f"{p}.shared.up"), device, dtype).unsqueeze(0)
-            self.shared_down = to_device(get(f"{p}.shared.down"), device, dtype).unsqueeze(0)
 
     def tile_for(self, tokens: int, dtype=None) -> int:
         """Rows of a tile of the layout: 16 for steps of single tokens; else 64, or 128 where the tensor-core product takes
@@ -88,7 +85,7 @@ class RoutedExperts(FeedForward):
         return 64
 
     def _fast(self, tile: int, dtype) -> bool:
-        return tile >= 64 and ops_tensor.grouped_bf16_supported(tile, self.ff, self.hidden, self.hidden, self.ff, dtype) and \
+        return ops_tensor.grouped_bf16_supported(tile, self.ff, self.hidden, self.hidden, self.ff, dtype) and \
             ops_tensor.grouped_bf16_supported(tile, self.hidden, self.ff, self.ff, self.hidden, dtype)
 
     def step_bytes(self, tokens: int, element_size: int) -> int:
@@ -125,13 +122,8 @@ class RoutedExperts(FeedForward):
         self._product(act, self.down, rows, tile, "none", fast, None, tile_expert, n_tiles)
         shared = None
         if self.shared_ff > 0:
-            st = 16 if T <= 16 else 64 if T < 1024 else 128
-            sfast = st >= 64 and ops_tensor.grouped_bf16_supported(st, self.shared_ff, self.hidden, self.hidden, self.shared_ff, h.dtype) \
-                and ops_tensor.grouped_bf16_supported(st, self.hidden, self.shared_ff, self.shared_ff, self.hidden, h.dtype)
-            if not sfast:
-                st = min(st, 64)
             sact = ctx.buffer((T, self.shared_ff))
-            self._product(h, self.shared_up, sact, st, self.activation, sfast)
+            self.shared_up.forward(h, sact, RELU2 if self.activation == "relu2" else STORE)
             shared = ctx.buffer((T, self.hidden))
-            self._product(sact, self.shared_down, shared, st, "none", sfast)
+            self.shared_down.forward(sact, shared, STORE)
         ops.moe_combine(rows, pair_row, weights, x, shared, sgate, accumulate)

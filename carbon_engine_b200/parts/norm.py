@@ -35,9 +35,9 @@ class RMSNorm(Norm):
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
 
-    def add_into(self, y: torch.Tensor, x: torch.Tensor) -> None:
-        """x += norm(y); both float32 [T, width]."""
-        ops.rmsnorm_add(y, self.weight, x, self.eps)
+    def add_into(self, y: torch.Tensor, x: torch.Tensor, rounded: Optional[torch.Tensor] = None) -> None:
+        """x += norm(y); both float32 [T, width].  ``rounded`` (bfloat16) receives the new x rounded."""
+        ops.rmsnorm_add(y, self.weight, x, self.eps, rounded)
 
 
 class GroupedRMSNorm(Norm):

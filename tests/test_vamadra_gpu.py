@@ -51,12 +51,16 @@ def tokens_of(rng, n, vocab):
 def test_norm_of_a_sublayers_output_added_into_the_residual():
     from carbon_engine_b200 import ops
     g = torch.Generator().manual_seed(1)
-    for T, W in ((5, 48), (1, 36), (70, 257)):
+    for T, W in ((5, 48), (1, 36), (70, 257), (9, 512), (3, 260)):
         y, x, w = torch.randn(T, W, generator=g) * 4, torch.randn(T, W, generator=g), torch.randn(W, generator=g) * 0.1
         want = x.double() + plain.norm_zero_centred(y.double(), w.double(), 1e-5)
         xd = x.cuda()
         ops.rmsnorm_add(y.cuda(), (1.0 + w).cuda(), xd, 1e-5)
         assert rel_err(xd.cpu().numpy(), want.numpy()) < 1e-6
+        # with the rounded copy that the next sublayer reads: the same residual, and its rounding
+        xd2, rounded = x.cuda(), torch.zeros(T, W, dtype=torch.bfloat16, device="cuda")
+        ops.rmsnorm_add(y.cuda(), (1.0 + w).cuda(), xd2, 1e-5, rounded)
+        assert torch.equal(xd2, xd) and torch.equal(rounded, xd.bfloat16())
 
 
 def test_router_kernel_picks_what_the_plain_router_picks():
@@ -147,13 +151,15 @@ def test_experts_products_over_the_layout_by_expert(dtype):
 
 
 def test_experts_products_on_the_tensor_core_kernel_that_loads_by_tma():
-    """The grouped product of steps of many tokens (bfloat16, tiles of 64 and 128 rows): the tokens' rows copied into the
+    """The grouped product in bfloat16 (tiles of 16 and 32 rows as steps of single tokens take them, of 64 and 128 rows for
+    steps of many tokens): the tokens' rows copied into the
     layout's order, then both products, against float64; output widths that are no multiple of the kernel's 128 features
     (an expert's last box then reaches into the next expert's rows), depths that are no multiple of 64, experts without a
     token, more tiles allotted than live; and one expert's product over rows as they lie (the shared expert)."""
     from carbon_engine_b200 import ops, ops_tensor
     g = torch.Generator().manual_seed(5)
-    for T, W, E, top, ff, tile in ((300, 64, 5, 2, 200, 64), (700, 136, 3, 1, 72, 128), (90, 256, 12, 3, 128, 64), (513, 128, 6, 4, 264, 128)):
+    for T, W, E, top, ff, tile in ((300, 64, 5, 2, 200, 64), (700, 136, 3, 1, 72, 128), (90, 256, 12, 3, 128, 64), (513, 128, 6, 4, 264, 128),
+                                   (4, 64, 9, 2, 96, 16), (21, 200, 7, 3, 40, 32), (1, 128, 5, 4, 136, 16)):
         h = (torch.randn(T, W, generator=g) * 0.5).bfloat16().cuda()
         up = (torch.randn(E, ff, W, generator=g) * 0.3).bfloat16().cuda()
         down = (torch.randn(E, W, ff, generator=g) * 0.3).bfloat16().cuda()
@@ -162,7 +168,7 @@ def test_experts_products_on_the_tensor_core_kernel_that_loads_by_tma():
         i32 = lambda n: torch.full((n,), -7, dtype=torch.int32, device="cuda")
         row_token, pair_row, tile_expert, n_tiles = i32(tiles * tile), i32(T * top), i32(tiles), i32(1)
         ops.moe_align(ids, E, tile, row_token, pair_row, tile_expert, n_tiles)
-        assert int(n_tiles[0]) < tiles
+        assert int(n_tiles[0]) <= tiles
         laid = torch.full((tiles * tile, W), float("nan"), dtype=torch.bfloat16, device="cuda")
         ops.moe_gather(h, row_token, n_tiles, tile, laid)
         live = int(n_tiles[0]) * tile
@@ -189,7 +195,33 @@ def test_experts_products_on_the_tensor_core_kernel_that_loads_by_tma():
     # sizes the kernel refuses go to the other kernels
     assert not ops_tensor.grouped_bf16_supported(64, 40, 36, 36, 40, torch.bfloat16)
     assert not ops_tensor.grouped_bf16_supported(64, 64, 64, 64, 64, torch.float32)
-    assert not ops_tensor.grouped_bf16_supported(16, 64, 64, 64, 64, torch.bfloat16)
+    assert not ops_tensor.grouped_bf16_supported(48, 64, 64, 64, 64, torch.bfloat16)
+
+
+def test_squared_relu_as_the_epilogue_of_every_product_kernel():
+    """The shared expert's first product: relu(x W^T)^2 from the float32 kernel, the tcgen05 kernels (one block, split
+    depth, CTA pairs) and the library product followed by the activation's own kernel."""
+    from carbon_engine_b200 import ops, ops_tensor
+    from carbon_engine_b200.parts import linear
+    g = torch.Generator().manual_seed(6)
+    for M, N, K in ((5, 24, 40), (8, 256, 4096), (70, 136, 64), (300, 512, 128), (1000, 384, 256)):
+        a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g) * 0.2
+        want = (torch.relu(a.double() @ w.double().T) ** 2).numpy()
+        out = torch.empty(M, N, device="cuda")
+        ops.gemm_plain(a.cuda(), w.cuda(), out, ops.GEMM_RELU2)
+        assert rel_err(out.cpu().numpy(), want) < 1e-5
+        ab, wb = a.cuda().bfloat16(), w.cuda().bfloat16()
+        wantb = (torch.relu(ab.double() @ wb.double().T) ** 2).cpu().numpy()
+        outb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        assert ops_tensor.gemm_bf16(ab, wb, outb, ops.GEMM_RELU2)
+        assert rel_err(outb.float().cpu().numpy(), wantb) < 1e-2
+        outb.zero_()
+        linear.BF16_BACKEND = "library"
+        try:
+            linear.matmul_nt(ab, wb, outb, linear.RELU2)
+        finally:
+            linear.BF16_BACKEND = "auto"
+        assert rel_err(outb.float().cpu().numpy(), wantb) < 1e-2
 
 
 def test_gate_per_head_on_the_product_per_head():
@@ -295,8 +327,8 @@ def test_whole_prompt_portions_and_decoding(tmp_path, name, dtype):
         assert err(got, want, clear) < TOL[dtype], cuts
         if dtype == "float32":
             assert np.array_equal(got, whole), cuts
-    if name in ("T", "V"):           # and single tokens take the small tiles of the other tensor-core product
-        assert ("moe_matmul_wmma_kernel" in ops.kernel_counts()) == (dtype == "bfloat16")
+    if name in ("T", "V"):           # single tokens take the same kernel with small tiles; float32 never
+        assert ("moe_matmul_plain_kernel" in ops.kernel_counts()) == (dtype == "float32")
     assert h.storage.manager.free_slots() == 4
     assert all(h.storage.manager.free_pages(g) == 16 for g in range(len(h.storage.groups)))
 
