@@ -168,7 +168,7 @@ def small_expert(w: Dict[str, torch.Tensor], p: str, h: torch.Tensor) -> torch.T
 def route(z: torch.Tensor, router: dict, margin: Optional[list] = None) -> Tuple[List[int], List[float]]:
     """One token's router logits -> the chosen experts and their weights.  ``margin`` receives how clear the choice was:
     the smallest gap between something chosen and something not (the last kept group and the first dropped one; the last
-    chosen expert and the first one passed over), in logits, as a fraction of the logits' spread."""
+    chosen expert and the first one passed over), in logits."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.softmax(z, dim=-1)
     allowed = list(range(E))
@@ -186,18 +186,24 @@ def route(z: torch.Tensor, router: dict, margin: Optional[list] = None) -> Tuple
     if top < len(ranked):
         gap = min(gap, float(z[ranked[top - 1]] - z[ranked[top]]))
     if margin is not None:
-        margin.append(gap / max(float(z.max() - z.min()), 1e-30))
+        margin.append(gap)
     total = sum(float(s[e]) for e in chosen) + 1e-20
     scale = float(router.get("scale", 1.0))
     return chosen, [float(s[e]) / total * scale for e in chosen]
 
 
 def moe_ffn(w: Dict[str, torch.Tensor], p: str, mlp: dict, h: torch.Tensor, margins: Optional[list] = None) -> torch.Tensor:
-    """``margins`` receives one number per token: see :func:`route`."""
+    """``margins`` receives one number per token: the gap of :func:`route` as a fraction of the size of what a router
+    logit is summed from (the root of the sum of its terms' squares: a rounding of the input moves a logit by a small
+    fraction of that)."""
     out = torch.zeros_like(h)
     z = h @ w[f"{p}.router"].T
     for t in range(h.shape[0]):
-        chosen, weights = route(z[t], mlp["router"], margins)
+        gap: list = []
+        chosen, weights = route(z[t], mlp["router"], gap)
+        if margins is not None:
+            size = float(torch.sqrt(((h[t][None, :] * w[f"{p}.router"]) ** 2).sum(-1)).max())
+            margins.append(gap[0] / max(size, 1e-30))
         for e, g in zip(chosen, weights):
             out[t] += g * small_expert(w, f"{p}.e{e}", h[t:t + 1])[0]
     if mlp.get("shared"):

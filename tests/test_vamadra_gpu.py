@@ -26,7 +26,7 @@ def plain_logits(folder, tokens):
 
 def plain_rows(folder, tokens, dtype="bfloat16"):
     """The plain logits and which rows to compare.  A token whose router's call is close (the gap between what is chosen
-    and what is not below 2 % of the logits' spread) may go to another expert once the activations are rounded to bfloat16,
+    and what is not below 2 % of the size of a logit's terms) may go to another expert once the activations are rounded to bfloat16,
     and its row then differs as a whole; such rows are left out in bfloat16.  float32 keeps every row."""
     cfg, w = plain.read_model(folder)
     margins = []
