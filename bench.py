@@ -268,11 +268,11 @@ def main() -> int:
                     help="run only the prefill of one prompt (for profiling, and for other prompt lengths) and print its time")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="with --prefill-only: tokens of the prompt (one step)")
     ap.add_argument("--profile", action="store_true",
-                    help="instead of the contract's line: time every kernel of a decode step and of a 2,048-token prefill "
+                    help="instead of the default JSON line: time every kernel of a decode step and of a 2,048-token prefill "
                          "with CUDA events (eager, kernels one after another) and print a table per kernel: launches, "
                          "microseconds, share, GB/s, TFLOP/s and the fraction of the measured peak")
     ap.add_argument("--between-steps", action="store_true",
-                    help="instead of the contract's line: the device activities between two decode steps through the entry "
+                    help="instead of the default JSON line: the device activities between two decode steps through the entry "
                          "point (pick, read-back copies, upload, token copy) and the steps' period")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of a short greedy continuation with float32")
     ap.add_argument("--sizes", default="1b,8b", help="with --workload compare-designs: which of the layer sizes "

@@ -52,7 +52,7 @@ def config(layers, width=40, vocab=97, eps=1e-5, max_positions=1024):
 
 _yarn = rot(dims=8, base=300.0, factor=3.0, original=24, fast=6.0, slow=0.5)
 CASES: Dict[str, dict] = {
-    # writer, mixture, two readers of layer 1 (as often seen), part of the rotated part turned
+    # writer, mixture, two readers of layer 1, part of the rotated part turned
     "A": config([layer(mlp=dense()), layer(rotation=_yarn, mlp=moe()), layer(rotation=_yarn, kv_from=1, heads=2, dim=6, vdim=10, mlp=dense(24)),
                  layer(rotation=_yarn, kv_from=1, mlp=moe(experts=4, top=1, groups=None, scale=None, shared=None))]),
     # a reader of layer 0 between two writers; a layer without a feed-forward; groups of one expert, all groups kept
