@@ -55,17 +55,23 @@ _SIGNATURES = {
     # in, in_stride, in_head, W, out, out_stride, out_head, gate, gate_stride, gate_head, dtype, M, H, N, K, stream
     "ce_head_matmul": (_i, [_p, _i, _i, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
-    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks, stream
-    "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p, _p]),
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks,
+    # out_scale, stream
+    "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p, _f, _p]),
+    # proj, q_out, k_pool, v_pool, dtype, wq, wk, head_scale, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
+    # T, ld, off_q, off_k, off_v, nh, nkv, d, dv, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps, stream
+    "ce_norm_rope_kvwrite": (_i, [_p] * 4 + [_i] + [_p] * 10 + [_i] * 15 + [_f, _p]),
     # d, dv, q_stride, q_head, ldk, ldv, alias
     "ce_masked_attention_mma_supported": (_i, [_i] * 7),
     # q, k_pool, v_pool, gate, out, positions, seq_slot, q_start, block_table, tiles, status, n_tiles, n_tokens, nh, nkv, d, dv,
-    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks, stream
-    "ce_masked_attention_mma": (_i, [_p] * 11 + [_i] * 16 + [_f, _f, _p, _p]),
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, sinks,
+    # out_scale, stream
+    "ce_masked_attention_mma": (_i, [_p] * 11 + [_i] * 16 + [_f, _f, _p, _f, _p]),
     "ce_gated_delta_prep_width": (_i, [_i, _i, _i, _i]),
     # proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, out_dtype, seq_of_token, seq_slot, q_start,
-    # T, B, ld, off_conv, off_b, H, G, d, dv, K, eps, stage, stream
-    "ce_gated_delta": (_i, [_p] * 12 + [_i] + [_p] * 3 + [_i] * 10 + [_f, _i, _p]),
+    # T, B, ld, off_conv, off_b, H, G, d, dv, K, eps, ld_dec, ld_gz, decay_mode, operands, rule, gate_act, out_scale,
+    # cos, sin, positions, status, rd, max_pos, stage, stream
+    "ce_gated_delta": (_i, [_p] * 12 + [_i] + [_p] * 3 + [_i] * 10 + [_f] + [_i] * 6 + [_f] + [_p] * 4 + [_i, _i, _i, _p]),
     # q, k_pool, v_pool, out, dtype, positions, seq_of_token, seq_slot, block_table, status,
     # T, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
     "ce_attention_generic": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p,

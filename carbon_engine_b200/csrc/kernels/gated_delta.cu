@@ -1,9 +1,17 @@
-// The gated delta rule with a decay per head and key channel: a recurrent mixer whose per-head state S [d, dv]
-// (key channel x value channel, float32) is carried from token to token:
+// Recurrent mixers whose per-head state S [d, dv] (key channel x value channel, float32) is carried from token to token.
+// The gated delta rule (rule 0):
 //
 //     S <- diag(g_t) S;    u_t = beta_t (v_t - S^T k_t);    S <- S + k_t u_t^T;    o_t = S^T q_t
 //
-// (the read-out sees the token's own write).  q, k and v come out of a short causal convolution over time per channel
+// (the read-out sees the token's own write), and the plain decaying sum of outer products, "retention" (rule 1): the same
+// with u_t = v_t.  The options are arguments, so that the family's mixers share the four kernels:
+//   decay     0: one per head and key channel from logits [T, H d];  1: one per head from logits [T, H];
+//             2: a constant per head (``a_log`` then holds the constants themselves, nothing is learned per token)
+//   operands  0: short convolution, SiLU, unit q and k (below);  1: no convolution: q and k are rotated over their first
+//             ``rd`` elements by the token's position (element i with i + rd/2), k times d^-1/2, v as projected
+//   gate      0: sigmoid, 1: SiLU of the gate logits;  the weight after the root mean square may be absent;  the stored
+//             result is multiplied by ``out_scale`` (the mixer's weight in a sum of mixers)
+// With the convolution:  q, k and v come out of a short causal convolution over time per channel
 // followed by SiLU; q and k are then brought to unit length per head (q also times d^-1/2); the decay is
 // g_t = exp(-exp(A_h) softplus(z_t + bias)) with z_t the token's decay logits (a product of their own);
 // beta_t = sigmoid of a projection, one per head.  Query/key head of value head h: h / (H / G).  Afterwards every
@@ -33,12 +41,12 @@ __device__ __forceinline__ float gd_softplus(float z) { return z > 20.f ? z : lo
 
 struct GatedDeltaArgs {
     const float* proj;           // [T, ld]: the convolution's inputs q | k | v from off_conv (C = 2 G d + H dv columns), beta logits at off_b
-    const float* dec;            // [T, H*d] decay logits before the bias
-    const float* gz;             // [T, H*dv] gate logits
-    const float* taps;           // [C, K] convolution weights, the last column the current token's
-    const float* a_log;          // [H]
-    const float* dt_bias;        // [H*d]
-    const float* norm_w;         // [dv]
+    const float* dec;            // decay logits before the bias, rows of ld_dec: [T, H*d] (decay 0) or [T, H] (decay 1); unused with decay 2
+    const float* gz;             // [T, H*dv] gate logits, rows of ld_gz
+    const float* taps;           // [C, K] convolution weights, the last column the current token's (operands 0)
+    const float* a_log;          // [H]; with decay 2 the heads' constant decays themselves
+    const float* dt_bias;        // [H*d] (decay 0) or [H] (decay 1)
+    const float* norm_w;         // [dv] or null
     float* prep;                 // [T, P]: q (G d) | k (G d) | v (H dv) | decay (H d) | beta (H); P padded to a multiple of 4
     float* raw;                  // [T, H*dv] o_t before the norm
     float* state;                // [slots, H, d, dv]
@@ -49,6 +57,14 @@ struct GatedDeltaArgs {
     const int* q_start;
     int ld, off_conv, off_b, H, G, d, dv, K, P;
     float eps;
+    int ld_dec, ld_gz;
+    int decay_mode, operands, rule, gate_act;
+    float out_scale;
+    const float* cos_table;      // [max_pos, rd/2] (operands 1; null or rd 0: no rotation)
+    const float* sin_table;
+    const int* positions;        // [T]
+    int* status;
+    int rd, max_pos;
 };
 
 // A token's heads of q, of k (unit vectors) and of v are dealt to the warps of gridDim.y blocks in turn (one block a token
@@ -65,6 +81,32 @@ __global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
     const float* kept = a.kept + (size_t)a.seq_slot[b] * (K - 1) * C;
     float* pw = a.prep + (size_t)t * a.P;
     float q_scale = rsqrtf((float)d);
+    int nthr = blockDim.x * gridDim.y, thr = blockIdx.y * blockDim.x + threadIdx.x;
+    if (a.operands == 1) {
+        // no convolution: q and k rotated by the position, k scaled, v as it is
+        const float* row = a.proj + (size_t)t * a.ld + a.off_conv;
+        int half = a.rd / 2, pos = a.positions[t];
+        bool rotate = a.cos_table != nullptr && half > 0;
+        if (rotate && (pos < 0 || pos >= a.max_pos)) {
+            if (thr == 0) atomicExch(a.status, 3);
+            rotate = false;
+        }
+        const float* cs = rotate ? a.cos_table + (size_t)pos * half : nullptr;
+        const float* sn = rotate ? a.sin_table + (size_t)pos * half : nullptr;
+        int nqk = 2 * G * d;
+        for (int e = thr; e < nqk; e += nthr) {
+            int i = e % d, base = e - i;
+            float x = row[e];
+            if (rotate && i < half) x = x * cs[i] - row[base + i + half] * sn[i];
+            else if (rotate && i < a.rd) x = x * cs[i - half] + row[base + i - half] * sn[i - half];
+            pw[e] = e >= G * d ? x * q_scale : x;
+        }
+        for (int e = thr; e < H * dv; e += nthr) pw[nqk + e] = row[nqk + e];
+        float* decay1 = pw + C;
+        for (int e = thr; e < H * d; e += nthr) decay1[e] = a.a_log[e / d];
+        for (int h = thr; h < H; h += nthr) decay1[H * d + h] = 1.0f;
+        return;
+    }
     // convolution + SiLU of channel c at this token
     auto conv = [&](int c) -> float {
         float y = 0.f;
@@ -97,9 +139,17 @@ __global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
         for (int c = lane; c < size; c += 32) pw[c0 + c] *= inv;
     }
     float* decay = pw + C;
-    int nthr = blockDim.x * gridDim.y, thr = blockIdx.y * blockDim.x + threadIdx.x;
-    for (int e = thr; e < H * d; e += nthr)
-        decay[e] = expf(-expf(a.a_log[e / d]) * gd_softplus(a.dec[(size_t)t * H * d + e] + a.dt_bias[e]));
+    if (a.decay_mode == 0) {
+        for (int e = thr; e < H * d; e += nthr)
+            decay[e] = expf(-expf(a.a_log[e / d]) * gd_softplus(a.dec[(size_t)t * a.ld_dec + e] + a.dt_bias[e]));
+    } else if (a.decay_mode == 1) {          // one decay per head, written to all its key channels
+        for (int e = thr; e < H * d; e += nthr) {
+            int h = e / d;
+            decay[e] = expf(-expf(a.a_log[h]) * gd_softplus(a.dec[(size_t)t * a.ld_dec + h] + a.dt_bias[h]));
+        }
+    } else {
+        for (int e = thr; e < H * d; e += nthr) decay[e] = a.a_log[e / d];
+    }
     for (int h = thr; h < H; h += nthr) decay[H * d + h] = gd_sigmoid(a.proj[(size_t)t * a.ld + a.off_b + h]);
 }
 
@@ -175,6 +225,7 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
     if (t_end <= t_begin) return;
     int ncols = min(GD_COLS, dv - col0);
+    const bool delta = a.rule == 0;
     int jj = tid / GD_R, g = tid % GD_R, j = col0 + jj;
     bool owner = jj < ncols;
     float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * dv;
@@ -252,7 +303,7 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
                 const float v_now = vj, beta_now = beta;
                 if (tok + 1 < GD_TILE) fetch(tok + 1);          // (rows past the tile's tokens hold older tokens: unused)
                 // over the column's lanes in rounds of four: every lane adds the same pairs, so all hold the same sum
-                {
+                if (delta) {
                     float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
                           e3 = __shfl_xor_sync(0xffffffffu, dot, 3);
                     dot = (dot + e1) + (e2 + e3);
@@ -261,7 +312,7 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
                     dot = (dot + f1) + (f2 + f3);
                     if (GD_R == 32) dot += __shfl_xor_sync(0xffffffffu, dot, 16);
                 }
-                float u = beta_now * (v_now - dot);
+                float u = delta ? beta_now * (v_now - dot) : v_now;         // the plain sum of outer products writes v itself
                 const float2 uu = make_float2(u, u);
                 float2 q01 = make_float2(0.f, 0.f), q23 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -300,7 +351,7 @@ __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
     int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int dv = a.dv, n = a.H * dv;
     const float* o = a.raw + (size_t)t * n;
-    const float* gz = a.gz + (size_t)t * n;
+    const float* gz = a.gz + (size_t)t * a.ld_gz;
     for (int h = warp; h < a.H; h += nwarp) {
         float ss = 0.f;
         for (int c = lane; c < dv; c += 32) ss = fmaf(o[h * dv + c], o[h * dv + c], ss);
@@ -308,7 +359,11 @@ __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
         float inv = 1.0f / sqrtf(ss / (float)dv + a.eps);
         for (int c = lane; c < dv; c += 32) {
             int col = h * dv + c;
-            CeType<T>::store((T*)a.out + (size_t)t * n + col, o[col] * inv * a.norm_w[c] * gd_sigmoid(gz[col]));
+            float z = gz[col], g = gd_sigmoid(z);
+            if (a.gate_act == 1) g *= z;
+            float y = o[col] * inv;
+            if (a.norm_w) y *= a.norm_w[c];
+            CeType<T>::store((T*)a.out + (size_t)t * n + col, y * g * a.out_scale);
         }
     }
 }
@@ -339,19 +394,29 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
                               const float* dt_bias, const float* norm_w, float* prep, float* raw, float* state, float* kept,
                               void* out, int out_dtype, const int* seq_of_token, const int* seq_slot, const int* q_start,
                               int T, int B, int ld, int off_conv, int off_b, int H, int G, int d, int dv, int K, float eps,
+                              int ld_dec, int ld_gz, int decay_mode, int operands, int rule, int gate_act, float out_scale,
+                              const float* cos_table, const float* sin_table, const int* positions, int* status, int rd, int max_pos,
                               int stage, cudaStream_t stream) {
     if (B == 0 || T == 0) return CE_OK;
     if (stage < 1 || stage > 4) return ce_fail(CE_ERR_ARG, "ce_gated_delta: stage %d", stage);
-    if (!proj || !dec || !gz || !taps || !a_log || !dt_bias || !norm_w || !prep || !raw || !state || !out || !seq_of_token ||
-        !seq_slot || !q_start || (K > 1 && !kept))
+    if (decay_mode < 0 || decay_mode > 2 || operands < 0 || operands > 1 || rule < 0 || rule > 1 || gate_act < 0 || gate_act > 1)
+        return ce_fail(CE_ERR_ARG, "ce_gated_delta: decay %d, operands %d, rule %d, gate %d", decay_mode, operands, rule, gate_act);
+    if (!proj || !gz || !a_log || !prep || !raw || !state || !out || !seq_of_token || !seq_slot || !q_start ||
+        (decay_mode != 2 && (!dec || !dt_bias)) || (operands == 0 && (!taps || (K > 1 && !kept))))
         return ce_fail(CE_ERR_ARG, "ce_gated_delta: null pointer");
+    if (operands == 1) {
+        if (K != 1 || decay_mode != 2) return ce_fail(CE_ERR_ARG, "ce_gated_delta: rotated operands come without a convolution and with constant decays");
+        if (rd < 0 || rd > d || rd % 2) return ce_fail(CE_ERR_SIZE, "ce_gated_delta: %d rotated elements of %d", rd, d);
+        if (rd > 0 && (!cos_table || !sin_table || !positions || !status)) return ce_fail(CE_ERR_ARG, "ce_gated_delta: no rotation tables");
+    }
     if (d <= 0 || d > 256 || dv <= 0) return ce_fail(CE_ERR_SIZE, "ce_gated_delta: head sizes %d / %d (keys up to 256)", d, dv);
     if (H <= 0 || G <= 0 || H % G || B > 65535 || K < 1 || K > 64)
         return ce_fail(CE_ERR_SIZE, "ce_gated_delta: %d heads, %d key heads, %d sequences, %d taps", H, G, B, K);
     if (out_dtype != CE_F32 && out_dtype != CE_BF16) return ce_fail(CE_ERR_ARG, "ce_gated_delta: unknown dtype %d", out_dtype);
     int P = ce_gated_delta_prep_width(H, G, d, dv);
     GatedDeltaArgs a{proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, seq_of_token, seq_slot, q_start,
-                     ld, off_conv, off_b, H, G, d, dv, K, P, eps};
+                     ld, off_conv, off_b, H, G, d, dv, K, P, eps, ld_dec, ld_gz, decay_mode, operands, rule, gate_act, out_scale,
+                     rd > 0 ? cos_table : nullptr, sin_table, positions, status, rd, max_pos};
     int heads = 2 * G + H;
     int threads = heads >= 8 ? 256 : 32 * heads;
     if (stage == 1) {

@@ -43,6 +43,118 @@ extern "C" int ce_value_mix(void* rows, int dtype, int stride, int off, int n, c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Operands of attention with a norm per head: proj [T, ld] float32 holds, per token, nh query heads of d from off_q, nkv key
+// heads of d from off_k and nkv value heads of dv from off_v.  Each query and key head is divided by its root mean square and
+// multiplied by a weight of size d (wq, wk; null: no norm), then rotated over its first rd elements (element i with
+// i + rd/2) by the token's position; query head h is also multiplied by head_scale[h] (a temperature per head folded into
+// the query; null: none).  Queries go to q_out [T, nh * d], keys and values to the token's place in the pools.  The values
+// may be the keys as projected (off_v = off_k, dv = d): they are read before the norm and the rotation.
+// One block per token; a warp per head in turn.
+// ---------------------------------------------------------------------------------------------
+struct NormRopeArgs {
+    const float* proj;
+    void* q_out;
+    void* k_pool;                // [num_pages, nkv, page_size, d]
+    void* v_pool;                // [num_pages, nkv, page_size, dv]
+    const float* wq;
+    const float* wk;
+    const float* head_scale;
+    const float* cos_table;      // [max_pos, rd/2] or null
+    const float* sin_table;
+    const int* positions;
+    const int* seq_of_token;
+    const int* seq_slot;
+    const int* block_table;
+    int* status;
+    int ld, off_q, off_k, off_v, nh, nkv, d, dv, rd, page_size, max_pages, num_pages, max_pos, write_kv;
+    float eps;
+};
+
+template <typename T>
+__global__ void norm_rope_kvwrite_kernel(NormRopeArgs a) {
+    ce_pdl_begin();
+    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int d = a.d, half = a.rd / 2;
+    int p = a.positions[t];
+    const float* row = a.proj + (size_t)t * a.ld;
+    bool rotate = a.cos_table != nullptr && half > 0;
+    if (rotate && (p < 0 || p >= a.max_pos)) {
+        if (threadIdx.x == 0) atomicExch(a.status, 3);
+        rotate = false;
+    }
+    int page = -1, off = 0;
+    if (a.write_kv) {
+        int slot = a.seq_slot[a.seq_of_token[t]];
+        page = a.block_table[(size_t)slot * a.max_pages + p / a.page_size];
+        off = p % a.page_size;
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) atomicExch(a.status, 2);
+            page = -1;
+        }
+    }
+    const float* cs = rotate ? a.cos_table + (size_t)p * half : nullptr;
+    const float* sn = rotate ? a.sin_table + (size_t)p * half : nullptr;
+    for (int hh = warp; hh < a.nh + a.nkv; hh += nwarp) {
+        bool is_q = hh < a.nh;
+        const float* src = row + (is_q ? a.off_q + hh * d : a.off_k + (hh - a.nh) * d);
+        const float* w = is_q ? a.wq : a.wk;
+        T* dst;
+        if (is_q) dst = (T*)a.q_out + ((size_t)t * a.nh + hh) * d;
+        else {
+            if (page < 0) continue;
+            dst = (T*)a.k_pool + (((size_t)page * a.nkv + (hh - a.nh)) * a.page_size + off) * d;
+        }
+        float inv = 1.0f;
+        if (w) {
+            float ss = 0.f;
+            for (int j = lane; j < d; j += 32) ss = fmaf(src[j], src[j], ss);
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+        }
+        float hs = is_q && a.head_scale ? a.head_scale[hh] : 1.0f;
+        for (int j = lane; j < d; j += 32) {
+            float x = w ? src[j] * inv * w[j] : src[j];
+            if (rotate && j < a.rd) {
+                int partner = j < half ? j + half : j - half;
+                float y = w ? src[partner] * inv * w[partner] : src[partner];
+                x = j < half ? x * cs[j] - y * sn[j] : x * cs[j - half] + y * sn[j - half];
+            }
+            CeType<T>::store(dst + j, x * hs);
+        }
+    }
+    if (page >= 0) {
+        for (int e = threadIdx.x; e < a.nkv * a.dv; e += blockDim.x) {
+            int h = e / a.dv, j = e % a.dv;
+            CeType<T>::store((T*)a.v_pool + (((size_t)page * a.nkv + h) * a.page_size + off) * a.dv + j, row[a.off_v + e]);
+        }
+    }
+}
+
+extern "C" int ce_norm_rope_kvwrite(const float* proj, void* q_out, void* k_pool, void* v_pool, int dtype, const float* wq,
+                                    const float* wk, const float* head_scale, const float* cos_table, const float* sin_table,
+                                    const int* positions, const int* seq_of_token, const int* seq_slot, const int* block_table,
+                                    int* status, int T, int ld, int off_q, int off_k, int off_v, int nh, int nkv, int d, int dv, int rd,
+                                    int page_size, int max_pages, int num_pages, int max_pos, int write_kv, float eps,
+                                    cudaStream_t stream) {
+    if (T == 0) return CE_OK;
+    if (!proj || !q_out || !positions || !seq_of_token || !seq_slot || !status) return ce_fail(CE_ERR_ARG, "ce_norm_rope_kvwrite: null pointer");
+    if (write_kv && (!k_pool || !v_pool || !block_table)) return ce_fail(CE_ERR_ARG, "ce_norm_rope_kvwrite: no cache to write to");
+    if (rd < 0 || rd > d || rd % 2) return ce_fail(CE_ERR_SIZE, "ce_norm_rope_kvwrite: %d rotated elements of %d", rd, d);
+    if (rd > 0 && (!cos_table || !sin_table)) return ce_fail(CE_ERR_ARG, "ce_norm_rope_kvwrite: no rotation tables");
+    if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0) return ce_fail(CE_ERR_SIZE, "ce_norm_rope_kvwrite: sizes");
+    NormRopeArgs a{proj, q_out, k_pool, v_pool, wq, wk, head_scale, rd > 0 ? cos_table : nullptr, sin_table, positions, seq_of_token,
+                   seq_slot, block_table, status, ld, off_q, off_k, off_v, nh, nkv, d, dv, rd, page_size, max_pages, num_pages, max_pos,
+                   write_kv, eps};
+    int heads = nh + nkv;
+    int threads = heads >= 8 ? 256 : 32 * heads;
+    ce_note("norm_rope_kvwrite_kernel");
+    if (dtype == CE_F32) ce_launch(norm_rope_kvwrite_kernel<float>, T, threads, 0, stream, a);
+    else if (dtype == CE_BF16) ce_launch(norm_rope_kvwrite_kernel<__nv_bfloat16>, T, threads, 0, stream, a);
+    else return ce_fail(CE_ERR_ARG, "ce_norm_rope_kvwrite: unknown dtype %d", dtype);
+    return ce_check_launch("ce_norm_rope_kvwrite");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Latent attention's operands.  proj [T, ld] float32 holds, per token, the query latent (qr columns from off_q)
 // and the key/value row (r latent columns, then dr columns of the rotated key part, from off_kv).
 //   cq[t]  = rms_norm(query latent) * wq                                    -> [T, qr], activation dtype
@@ -346,6 +458,7 @@ struct MaskedAttnArgs {
     const float* sinks;          // [nh] or null: exp(sinks[h]) joins the softmax's denominator, with no key and no value
     int T, nh, nkv, d, dv, q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first;
     float scale, softcap;
+    float out_scale;             // the stored result is multiplied by this (the mixer's weight in a sum of mixers)
 };
 
 template <typename T>
@@ -431,7 +544,7 @@ __global__ void masked_attention_kernel(MaskedAttnArgs a) {
     for (int i = 0; i < MA_MAX_ACC; ++i) {
         int j = tid + i * MA_THREADS;
         if (j < dv) {
-            float o = acc[i] * inv;
+            float o = acc[i] * inv * a.out_scale;
             if (a.gate) o *= ma_sigmoid(CeType<T>::load((const T*)a.gate + (size_t)t * a.gate_stride + (size_t)h * dv + j));
             CeType<T>::store(orow + j, o);
         }
@@ -442,7 +555,7 @@ extern "C" int ce_masked_attention(const void* q, const void* k_pool, const void
                                    const int* positions, const int* seq_of_token, const int* seq_slot, const int* block_table,
                                    int* status, int T, int nh, int nkv, int d, int dv, int q_stride, int q_head, int ldk, int ldv,
                                    int gate_stride, int page_size, int max_pages, int num_pages, int window, int keep_first,
-                                   float scale, float softcap, const float* sinks, cudaStream_t stream) {
+                                   float scale, float softcap, const float* sinks, float out_scale, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !seq_of_token || !seq_slot || !block_table || !status)
         return ce_fail(CE_ERR_ARG, "ce_masked_attention: null pointer");
@@ -451,7 +564,8 @@ extern "C" int ce_masked_attention(const void* q, const void* k_pool, const void
     if (nkv <= 0 || nh % nkv != 0) return ce_fail(CE_ERR_SIZE, "ce_masked_attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     if (ldk < d || ldv < dv || nh > 65535) return ce_fail(CE_ERR_SIZE, "ce_masked_attention: a pool's rows are shorter than a head");
     MaskedAttnArgs a{q, k_pool, v_pool, gate, out, positions, seq_of_token, seq_slot, block_table, status, sinks, T, nh, nkv, d, dv,
-                     q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap};
+                     q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap,
+                     out_scale};
     size_t smem = (d + MA_THREADS + 32) * sizeof(float) + MA_THREADS * sizeof(long long);
     dim3 grid(T, nh);
     ce_note("masked_attention_kernel");

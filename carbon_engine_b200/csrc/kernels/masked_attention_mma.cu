@@ -47,6 +47,7 @@ struct MaskedMmaArgs {
     int slice;                   // value columns a block takes (a multiple of 16)
     int share;                   // 1: four K/V buffers are there, and blocks of at most 16 rows spread their key tiles over the warps
     float scale, softcap;
+    float out_scale;             // the stored result is multiplied by this (the mixer's weight in a sum of mixers)
 };
 
 __device__ __forceinline__ void mm_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
@@ -360,7 +361,7 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 2)) masked_attent
         l_a = l_a * sh_a + exp2f(sk_a - big_a);
         l_b = l_b * sh_b + exp2f(sk_b - big_b);
     }
-    float i_a = l_a > 0.f ? sh_a / l_a : 0.f, i_b = l_b > 0.f ? sh_b / l_b : 0.f;
+    float i_a = (l_a > 0.f ? sh_a / l_a : 0.f) * a.out_scale, i_b = (l_b > 0.f ? sh_b / l_b : 0.f) * a.out_scale;
 #pragma unroll
     for (int nt = 0; nt < DVT; ++nt) {
         if (nt * 8 < ncol) {
@@ -442,7 +443,7 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
                                        const int* tiles, int* status, int n_tiles, int n_tokens, int nh, int nkv, int d, int dv,
                                        int q_stride, int q_head, int ldk, int ldv, int gate_stride, int page_size, int max_pages,
                                        int num_pages, int window, int keep_first, float scale, float softcap, const float* sinks,
-                                       cudaStream_t stream) {
+                                       float out_scale, cudaStream_t stream) {
     if (n_tiles == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !seq_slot || !q_start || !block_table || !tiles || !status)
         return ce_fail(CE_ERR_ARG, "ce_masked_attention_mma: null pointer");
@@ -470,7 +471,8 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
     }
     MaskedMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
                     (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, sinks, nh, nkv, d, dv, q_stride, q_head,
-                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, buffers == 4, scale, softcap};
+                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, buffers == 4, scale, softcap,
+                    out_scale};
     dim3 grid(n_tiles * pack, nh / pack, (dv + slice - 1) / slice);
     size_t smem = mm_smem_bytes(d, slice, alias, buffers);
     int bn = mm_key_tile(d, slice, alias, buffers);

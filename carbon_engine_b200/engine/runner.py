@@ -102,9 +102,9 @@ class ModelRunner:
         # one planner per kind of mixer that lays out tables of its own for a step
         self._planners = {}
         for block in model.blocks:
-            key = getattr(block.mixer, "plan_key", None)
-            if key is not None and key not in self._planners:
-                self._planners[key] = block.mixer
+            for mixer in block.mixer.planners():
+                if mixer.plan_key not in self._planners:
+                    self._planners[mixer.plan_key] = mixer
         sections = [s for m in self._planners.values() for s in m.step_sections(self.max_step_tokens, storage.max_requests)]
         self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device, sections)
         self.fast_attention = True

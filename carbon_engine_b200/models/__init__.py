@@ -1,2 +1,2 @@
 """Architectures the engine can build.  Importing this package registers them."""
-from . import lunerax, munizen, qwen3, vamadra  # noqa: F401
+from . import lunerax, munizen, pugozen, qwen3, vamadra  # noqa: F401

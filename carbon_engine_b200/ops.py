@@ -379,7 +379,7 @@ def head_matmul(inp, in_head: int, w, out, out_head: int, heads: int, n: int, k:
 
 def masked_attention(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_of_token, seq_slot,
                      block_table, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int, keep_first: int,
-                     scale: float, softcap: float, sinks=None) -> None:
+                     scale: float, softcap: float, sinks=None, out_scale: float = 1.0) -> None:
     """Softmax attention in float32 arithmetic with separate key and value head sizes, a tanh cap on the scores
     (0: none), a window (0: none) that keeps the first ``keep_first`` keys visible, and an optional sigmoid gate per
     output element.  ``v_pool`` may be the key pool itself (``ldv`` = ``ldk``): the values are then the leading
@@ -392,7 +392,7 @@ def masked_attention(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, o
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), dtype_code(out.dtype), _ptr(positions), _ptr(seq_of_token),
         _ptr(seq_slot), _ptr(block_table), _ptr(status), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
         gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
-        float(scale), float(softcap), _ptr(sinks), _stream()))
+        float(scale), float(softcap), _ptr(sinks), float(out_scale), _stream()))
 
 
 def _check_sinks(sinks, nh: int) -> None:
@@ -406,7 +406,7 @@ def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, 
 
 def masked_attention_mma(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_slot, q_start, block_table,
                          tiles, n_tiles: int, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int,
-                         keep_first: int, scale: float, softcap: float, sinks=None) -> None:
+                         keep_first: int, scale: float, softcap: float, sinks=None, out_scale: float = 1.0) -> None:
     """:func:`masked_attention` on the tensor cores (bfloat16) for tiles of 64 query tokens: ``tiles`` holds (sequence, first
     token within the sequence's tokens of the step) pairs.  ``gate`` holds bfloat16 logits."""
     _need(k_pool, "k_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
@@ -417,31 +417,98 @@ def masked_attention_mma(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gat
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), _ptr(positions), _ptr(seq_slot), _ptr(q_start), _ptr(block_table),
         _ptr(tiles), _ptr(status), int(n_tiles), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
         gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
-        float(scale), float(softcap), _ptr(sinks), _stream()))
+        float(scale), float(softcap), _ptr(sinks), float(out_scale), _stream()))
+
+
+def norm_rope_kvwrite(proj, q_out, k_pool, v_pool, wq, wk, head_scale, cos, sin, positions, seq_of_token, seq_slot, block_table,
+                      status, off_q: int, off_k: int, off_v: int, nh: int, nkv: int, d: int, dv: int, rotary_dim: int,
+                      page_size: int, eps: float, write_kv: bool = True) -> None:
+    """Operands of attention with a norm per head, from float32 rows ``proj``: query heads (from ``off_q``) and key heads
+    (from ``off_k``) divided by their root mean square times ``wq`` / ``wk`` (None: no norm), rotated over their first
+    ``rotary_dim`` elements (element i with i + rotary_dim/2), queries times ``head_scale[h]`` (None: no factor) into
+    ``q_out`` [T, nh * d], keys and the values (``nkv`` heads of ``dv`` from ``off_v``; ``off_v`` = ``off_k``: the keys as
+    projected) into the pages."""
+    _need(q_out, "q_out")
+    if proj.dtype != torch.float32 or proj.stride(-1) != 1:
+        raise KernelError("norm_rope_kvwrite: proj must be float32 rows")
+    for name, t in (("wq", wq), ("wk", wk), ("head_scale", head_scale), ("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    T = q_out.shape[0]
+    if q_out.shape[1] != nh * d or (wq is not None and wq.numel() != d) or (wk is not None and wk.numel() != d) or \
+            (head_scale is not None and head_scale.numel() != nh) or proj.shape[1] < max(off_q + nh * d, off_k + nkv * d, off_v + nkv * dv):
+        raise KernelError("norm_rope_kvwrite: sizes do not fit")
+    if cos is not None and cos.shape[1] != rotary_dim // 2:
+        raise KernelError("norm_rope_kvwrite: rotary table width is not rotary_dim / 2")
+    if write_kv:
+        _need(k_pool, "k_pool", q_out.dtype); _need(v_pool, "v_pool", q_out.dtype)
+        if tuple(k_pool.shape[1:]) != (nkv, page_size, d) or tuple(v_pool.shape[1:]) != (nkv, page_size, dv):
+            raise KernelError(f"norm_rope_kvwrite: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit "
+                              f"{nkv} x {d} keys and {nkv} x {dv} values in pages of {page_size}")
+    _ok(kernels().ce_norm_rope_kvwrite(
+        _ptr(proj), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), dtype_code(q_out.dtype), _ptr(wq), _ptr(wk), _ptr(head_scale),
+        _ptr(cos), _ptr(sin), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status), T,
+        proj.stride(0), int(off_q), int(off_k), int(off_v), nh, nkv, d, dv, rotary_dim if cos is not None else 0, page_size,
+        block_table.shape[1] if block_table is not None else 0, k_pool.shape[0] if k_pool is not None else 0,
+        cos.shape[0] if cos is not None else 0, 1 if write_kv else 0, float(eps), _stream()))
 
 
 def gated_delta_prep_width(heads: int, key_heads: int, d: int, dv: int) -> int:
     return kernels().ce_gated_delta_prep_width(heads, key_heads, d, dv)
 
 
+DECAY_PER_CHANNEL, DECAY_PER_HEAD, DECAY_CONSTANT = 0, 1, 2
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
 def gated_delta(proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, seq_of_token, seq_slot, q_start,
-                n_seqs: int, off_conv: int, off_b: int, heads: int, key_heads: int, d: int, dv: int, n_taps: int, eps: float) -> None:
-    """The gated delta rule with a decay per key channel over each sequence's tokens of the step, from and to ``state``
-    [slots, heads, d, dv] and the convolution's kept rows ``kept`` [slots, taps - 1, C] (both float32).  ``proj`` float32
-    [T, ld] holds the convolution's inputs q | k | v from ``off_conv`` and the beta logits at ``off_b``; ``dec``
-    [T, heads * d] the decay logits, ``gz`` [T, heads * dv] the gate logits.  Four launches: prepare, keep, walk, finish."""
+                n_seqs: int, off_conv: int, off_b: int, heads: int, key_heads: int, d: int, dv: int, n_taps: int, eps: float,
+                decay: int = DECAY_PER_CHANNEL, gate: int = GATE_SIGMOID, delta: bool = True, out_scale: float = 1.0,
+                rotation=None) -> None:
+    """The recurrent mixers with a matrix state per head over each sequence's tokens of the step, from and to ``state``
+    [slots, heads, d, dv] (float32).  ``proj`` float32 [T, ld] holds q | k | v from ``off_conv`` and the beta logits at
+    ``off_b``; ``gz`` the gate logits [T, heads * dv] (rows of any stride).
+
+    ``delta``: the gated delta rule (True) or the plain decaying sum of outer products, which writes v itself (False).
+    ``decay``: per head and key channel from logits ``dec`` [T, heads * d] with ``dt_bias`` [heads * d]; per head from
+    logits ``dec`` [T, heads] with ``dt_bias`` [heads]; or constant, ``a_log`` then holding the heads' decays themselves.
+    ``rotation`` None: q, k, v pass the short convolution (``taps`` [C, n_taps], the kept rows ``kept`` [slots, taps - 1, C])
+    and SiLU, and q and k become unit vectors; ``rotation`` = (cos, sin, rotary_dim, positions, status): no convolution, q and
+    k are rotated by the position and k is multiplied by d^-1/2 (with constant decays).  ``gate``: sigmoid or SiLU of the
+    gate logits; ``norm_w`` None: no weight after the root mean square; ``out_scale`` multiplies what is stored.
+    Four launches: prepare, keep, walk, finish."""
     _need(state, "state", torch.float32); _need(out, "out")
-    for name, t in (("dec", dec), ("gz", gz), ("taps", taps), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w),
-                    ("prep", prep), ("raw", raw)):
-        _need(t, name, torch.float32)
-    if proj.dtype != torch.float32 or proj.stride(-1) != 1:
-        raise KernelError("gated_delta: proj must be float32 rows")
+    for name, t in (("taps", taps), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w), ("prep", prep), ("raw", raw)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    for name, t in (("proj", proj), ("dec", dec), ("gz", gz)):
+        if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1 or not t.is_cuda):
+            raise KernelError(f"gated_delta: {name} must be float32 rows on the GPU")
     T, C = out.shape[0], 2 * key_heads * d + heads * dv
     P = gated_delta_prep_width(heads, key_heads, d, dv)
-    if tuple(state.shape[1:]) != (heads, d, dv) or out.shape[1] != heads * dv or dec.shape != (T, heads * d) or \
-            gz.shape != (T, heads * dv) or prep.numel() < T * P or raw.numel() < T * heads * dv or tuple(taps.shape) != (C, n_taps) or \
-            (n_taps > 1 and tuple(kept.shape[1:]) != (n_taps - 1, C)):
+    n_dec = {DECAY_PER_CHANNEL: heads * d, DECAY_PER_HEAD: heads}.get(decay)
+    if tuple(state.shape[1:]) != (heads, d, dv) or out.shape[1] != heads * dv or tuple(gz.shape) != (T, heads * dv) or \
+            prep.numel() < T * P or raw.numel() < T * heads * dv or a_log.numel() != heads or \
+            (norm_w is not None and norm_w.numel() != dv):
         raise KernelError("gated_delta: sizes do not fit")
+    if n_dec is not None and (dec is None or tuple(dec.shape) != (T, n_dec) or dt_bias is None or dt_bias.numel() != n_dec):
+        raise KernelError("gated_delta: the decay's logits or bias do not fit")
+    cos = sin = positions = status = None
+    rd = max_pos = 0
+    if rotation is None:
+        if tuple(taps.shape) != (C, n_taps) or (n_taps > 1 and tuple(kept.shape[1:]) != (n_taps - 1, C)):
+            raise KernelError("gated_delta: the convolution's sizes do not fit")
+    else:
+        cos, sin, rd, positions, status = rotation
+        if n_taps != 1 or decay != DECAY_CONSTANT:
+            raise KernelError("gated_delta: rotated operands come without a convolution and with constant decays")
+        if cos is not None:
+            _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32)
+            if cos.shape[1] != rd // 2:
+                raise KernelError("gated_delta: rotary table width is not rotary_dim / 2")
+            max_pos = cos.shape[0]
+        else:
+            rd = 0
     prof, work = profiling(), None
     if prof is not None:
         work, prof._work = prof._work, (0, 0)            # the caller's figures belong to the walk
@@ -453,7 +520,10 @@ def gated_delta(proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, k
         _ok(kernels().ce_gated_delta(_ptr(proj), _ptr(dec), _ptr(gz), _ptr(taps), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
                                      _ptr(prep), _ptr(raw), _ptr(state), _ptr(kept), _ptr(out), dtype_code(out.dtype),
                                      _ptr(seq_of_token), _ptr(seq_slot), _ptr(q_start), T, n_seqs, proj.stride(0), int(off_conv),
-                                     int(off_b), heads, key_heads, d, dv, n_taps, float(eps), stage, _stream()))
+                                     int(off_b), heads, key_heads, d, dv, n_taps, float(eps),
+                                     dec.stride(0) if dec is not None else 0, gz.stride(0), int(decay), 0 if rotation is None else 1,
+                                     0 if delta else 1, int(gate), float(out_scale), _ptr(cos), _ptr(sin), _ptr(positions),
+                                     _ptr(status), int(rd), int(max_pos), stage, _stream()))
 
 
 def attention_generic(q, q_stride: int, k_pool, v_pool, out, positions, seq_of_token, seq_slot, block_table,

@@ -133,6 +133,11 @@ class Mixer(Part):
     def cache_spec(self) -> CacheSpec:
         return None
 
+    def planners(self) -> List["Mixer"]:
+        """The mixers whose :meth:`plan_step` the step function has to call for this one: itself if it names a
+        ``plan_key``; a mixer made of several returns theirs."""
+        return [self] if self.plan_key is not None else []
+
     def step_sections(self, max_tokens: int, max_seqs: int) -> List[Tuple[str, int]]:
         """(name, int32 count) of the sections this kind of mixer wants in the step's pinned buffer
         (uploaded with the step in one copy, at addresses that never change)."""

@@ -1,5 +1,6 @@
 """Arrangements of parts in a layer.  Pre-norm: x += mixer(norm1(x)); x += ffn(norm2(x))
-(src/model/mod.rs:645-650).  Output-norm: x += norm1(mixer(x)); x += norm2(ffn(x))."""
+(src/model/mod.rs:645-650).  Output-norm: x += norm1(mixer(x)); x += norm2(ffn(x)).  Parallel: h = norm1(x);
+x += mixer(h) + ffn(h)."""
 from __future__ import annotations
 
 from typing import List, Optional
@@ -37,6 +38,29 @@ class PreNormBlock(Block):
             self.ffn.forward(ctx, h, x)
         if self.after is not None:
             self.after.forward(ctx, x)
+
+
+class ParallelBlock(Block):
+    """One norm, and both sublayers read its output: h = norm(x); x += mixer(h) + ffn(h).  ``ffn`` None: the layer has only the
+    mixer.  Both sublayers add into the float32 residual, the mixer first."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward] = None):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm, self.mixer, self.ffn) if p is not None]
+
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        h = tokens * self.norm.width * element_size if hasattr(self.norm, "width") else 0
+        ffn = self.ffn.step_bytes(tokens, element_size) if self.ffn is not None else 0
+        return h + max(self.mixer.step_bytes(tokens, element_size), ffn)
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> None:
+        h = ctx.buffer(tuple(x.shape))
+        self.norm.forward(x, h)
+        self.mixer.forward(ctx, h, x, cache)
+        if self.ffn is not None:
+            self.ffn.forward(ctx, h, x)
 
 
 class OutputNormBlock(Block):

@@ -41,10 +41,10 @@ def plan_query_tiles(ctx, section: str, tile: int) -> MaskedAttentionPlan:
 
 
 def attend(ctx, plan, q, q_head, cache, ldk, ldv, v_pool, gate, out, table, nh, nkv, d, dv, window, keep_first, scale, softcap,
-           sinks=None):
+           sinks=None, out_scale=1.0):
     """The attention of both mixers of this family: the tensor-core kernel where it takes the sizes (bfloat16), else
     the float32-arithmetic kernel.  ``sinks`` (float32 [nh] or None): a learned number per head whose exponential joins
-    the softmax's denominator without a key or a value."""
+    the softmax's denominator without a key or a value.  ``out_scale`` multiplies what is stored."""
     prof = ops.profiling()
     if prof is not None:
         el, keys, pairs = q.element_size(), 0, 0
@@ -60,10 +60,10 @@ def attend(ctx, plan, q, q_head, cache, ldk, ldv, v_pool, gate, out, table, nh, 
             ops.masked_attention_mma_supported(d, dv, q.stride(0), q_head, ldk, ldv, v_pool is cache.k_pool):
         ops.masked_attention_mma(q, q_head, cache.k_pool, v_pool, ldk, ldv, gate, out, ctx.positions, ctx.seq_slot, ctx.q_start,
                                  table, plan.tiles, plan.n_tiles, ctx.status, nh, nkv, d, dv, cache.page_size, window, keep_first,
-                                 scale, softcap, sinks)
+                                 scale, softcap, sinks, out_scale)
         return
     ops.masked_attention(q, q_head, cache.k_pool, v_pool, ldk, ldv, gate, out, ctx.positions, ctx.seq_of_token, ctx.seq_slot,
-                         table, ctx.status, nh, nkv, d, dv, cache.page_size, window, keep_first, scale, softcap, sinks)
+                         table, ctx.status, nh, nkv, d, dv, cache.page_size, window, keep_first, scale, softcap, sinks, out_scale)
 
 
 class GatedWindowAttention(Mixer):

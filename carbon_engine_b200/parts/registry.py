@@ -10,13 +10,16 @@ from typing import Callable, Dict
 from .attention import PagedAttention
 from .delta_rule import GeneralDeltaRule
 from .diff_attention import DifferentialAttention
-from .gated_delta import ChannelGatedDelta
+from .combine import SummedMixers
+from .gated_delta import ChannelGatedDelta, HeadGatedDelta
 from .latent_attention import LatentAttention
 from .masked_attention import GatedWindowAttention
-from .mlp import GatedMLP
+from .mlp import DenseMLP, GatedMLP
 from .moe import RoutedExperts
 from .norm import GroupedRMSNorm, LayerNorm, RMSNorm
+from .retention import Retention
 from .rope import NoPositionEncoding, RotaryEmbedding
+from .sink_attention import SinkAttention
 
 _KINDS: Dict[str, Dict[str, Callable]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}}
 
@@ -53,7 +56,12 @@ register_mixer("general_delta", GeneralDeltaRule)
 register_mixer("gated_window_attention", GatedWindowAttention)
 register_mixer("latent_attention", LatentAttention)
 register_mixer("channel_gated_delta", ChannelGatedDelta)
+register_mixer("head_gated_delta", HeadGatedDelta)
+register_mixer("retention", Retention)
+register_mixer("sink_attention", SinkAttention)
+register_mixer("summed_mixers", SummedMixers)
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("dense_mlp", DenseMLP)
 register_feed_forward("routed_experts", RoutedExperts)
 register_norm("rmsnorm", RMSNorm)
 register_norm("grouped_rmsnorm", GroupedRMSNorm)
