@@ -112,8 +112,8 @@ def cmd_tiny_model(a) -> int:
     from . import models  # noqa: F401
     from .config.qwen3 import Qwen3Config
     from .weights.loader import write_random_model
-    if a.arch not in ("qwen3", "munizen", "lunerax", "vamadra"):
-        raise SystemExit(f"--arch {a.arch}: qwen3, munizen, lunerax and vamadra are built")
+    if a.arch not in ("qwen3", "munizen", "lunerax", "vamadra", "pugozen"):
+        raise SystemExit(f"--arch {a.arch}: qwen3, munizen, lunerax, vamadra and pugozen are built")
     heads = a.heads or 4
     head_dim = a.head_dim or 16
     store = {"f32": torch.float32, "bf16": torch.bfloat16}.get(a.dtype)
@@ -125,6 +125,15 @@ def cmd_tiny_model(a) -> int:
         cfg = sketch_config(a.vocab, a.hidden, a.layers, heads, a.kv_heads or max(1, heads // 2), head_dim,
                             a.intermediate or 2 * a.hidden, window=a.mask_size, side_dim=a.side_dim, max_positions=a.max_positions,
                             eps=a.rms_norm_eps, rope_base=a.rope_theta)
+        print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
+        return 0
+    if a.arch == "pugozen":
+        # layers go delta rule, parallel (attention beside the delta rule), parallel, retention; --shared-from: the layers
+        # from that index on run the weights of the layer that many places before them
+        from .config.pugozen import sketch_config
+        cfg = sketch_config(a.vocab, a.hidden, a.layers, heads, a.kv_heads or max(1, heads // 2), head_dim,
+                            a.intermediate or 2 * a.hidden, max_positions=a.max_positions, eps=a.rms_norm_eps,
+                            rope_base=a.rope_theta, shared_from=a.shared_from)
         print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
         return 0
     if a.arch == "vamadra":
@@ -197,7 +206,9 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     t = sub.add_parser("tiny-model", help="write a small random model folder")
     t.add_argument("--out", required=True)
-    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen | lunerax | vamadra")
+    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen | lunerax | vamadra | pugozen")
+    t.add_argument("--shared-from", type=int, default=0,
+                   help="pugozen: layers from this index on run the weights of the layer this many places before (0: none)")
     t.add_argument("--experts", type=int, default=8, help="vamadra: experts of a mixture layer")
     t.add_argument("--top-experts", type=int, default=2, help="vamadra: experts a token uses")
     t.add_argument("--expert-groups", type=int, default=4, help="vamadra: groups the experts form (half of them stay eligible)")
