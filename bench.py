@@ -211,15 +211,39 @@ def vamadra_config(width, heads, kv_heads, ff, layers, vocab):
                                     "norm": {"eps": 1e-6}, "max_position_embeddings": 8192})
 
 
+def pugozen_config(width, heads, kv_heads, ff, layers, vocab):
+    """A Pugozen model of the usual proportions at the Qwen3 model's layer sizes: layers go delta rule with a decay per head
+    (state heads of 128 x 128, half as many key heads, 4 taps), the pair (attention with heads of 128 whose values are the
+    projected keys, a quarter of a head rotated, a temperature and a sink per head, beside the delta rule with a decay per
+    key channel: state heads of 128 x 128, 3 taps), the pair again, retention (state heads of 128 x 128, whole heads rotated);
+    every layer with the dense squared-ReLU feed-forward; no layer shares weights."""
+    from carbon_engine_b200.config.pugozen import PugozenConfig
+    ffn = {"kind": "dense", "ff": ff}
+    n = width // 128
+    delta = {"type": "delta", "mlp": ffn, "mixer": {"heads": n, "kv_heads": max(1, n // 2), "dim": 128, "vdim": 128, "conv": 4}}
+    pair = {"type": "parallel", "mlp": ffn,
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                               "rot": {"dims": 32, "base": 1e6}},
+                      "right": {"heads": n, "kv_heads": n, "dim": 128, "vdim": 128, "conv": 3, "a_rank": 64, "g_rank": 64},
+                      "left_scale": 0.8, "right_scale": 0.5}}
+    retention = {"type": "retention", "mlp": ffn,
+                 "mixer": {"heads": n, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - (6 * j) // n) for j in range(n)],
+                           "rot": {"dims": 128, "base": 1e6}}}
+    kinds = (delta, pair, pair, retention)
+    return PugozenConfig.from_dict({"architecture": "Pugozen", "vocab": vocab, "width": width,
+                                    "layers": [kinds[i % 4] for i in range(layers)], "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": float(width) ** 0.5}, "max_position_embeddings": 8192})
+
+
 def compare_designs(args, BenchHarness, pk) -> int:
-    """Prefill and decode throughput of the engine's other designs (--designs: munizen, lunerax, vamadra) beside the Qwen3 dense
+    """Prefill and decode throughput of the engine's other designs (--designs: munizen, lunerax, vamadra, pugozen) beside the Qwen3 dense
     design at equal layer sizes (random weights, a few layers), with the kernels of each and their distance from the roofline."""
     import torch
-    makers = {"munizen": munizen_config, "lunerax": lunerax_config, "vamadra": vamadra_config}
+    makers = {"munizen": munizen_config, "lunerax": lunerax_config, "vamadra": vamadra_config, "pugozen": pugozen_config}
     designs = [x for x in args.designs.split(",") if x != "qwen3"]
     for x in designs:
         if x not in makers:
-            raise SystemExit(f"--designs {x}: munizen, lunerax, vamadra and qwen3 are built")
+            raise SystemExit(f"--designs {x}: munizen, lunerax, vamadra, pugozen and qwen3 are built")
     layers = args.layers if args.layers != SIZES_8B["num_hidden_layers"] else 4
     vocab, out = 32768, {}
     for name in args.sizes.split(","):
@@ -278,7 +302,7 @@ def main() -> int:
     ap.add_argument("--sizes", default="1b,8b", help="with --workload compare-designs: which of the layer sizes "
                     "1b, 4b, 8b (width / heads / feed-forward of models of about that size), with commas between them")
     ap.add_argument("--designs", default="munizen,qwen3", help="with --workload compare-designs: the designs set beside one another "
-                    "(munizen, lunerax, vamadra; qwen3 is always the last)")
+                    "(munizen, lunerax, vamadra, pugozen; qwen3 is always the last)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b", "compare-designs"],
                     help="decode: the headline line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
                          "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "

@@ -49,7 +49,7 @@ extern "C" int ce_value_mix(void* rows, int dtype, int stride, int off, int n, c
 // i + rd/2) by the token's position; query head h is also multiplied by head_scale[h] (a temperature per head folded into
 // the query; null: none).  Queries go to q_out [T, nh * d], keys and values to the token's place in the pools.  The values
 // may be the keys as projected (off_v = off_k, dv = d): they are read before the norm and the rotation.
-// One block per token; a warp per head in turn.
+// A warp per head in turn.
 // ---------------------------------------------------------------------------------------------
 struct NormRopeArgs {
     const float* proj;
@@ -73,7 +73,8 @@ struct NormRopeArgs {
 template <typename T>
 __global__ void norm_rope_kvwrite_kernel(NormRopeArgs a) {
     ce_pdl_begin();
-    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int t = blockIdx.x, lane = threadIdx.x & 31, nwarp = (blockDim.x >> 5) * gridDim.y;
+    int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int d = a.d, half = a.rd / 2;
     int p = a.positions[t];
     const float* row = a.proj + (size_t)t * a.ld;
@@ -123,7 +124,7 @@ __global__ void norm_rope_kvwrite_kernel(NormRopeArgs a) {
         }
     }
     if (page >= 0) {
-        for (int e = threadIdx.x; e < a.nkv * a.dv; e += blockDim.x) {
+        for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < a.nkv * a.dv; e += blockDim.x * gridDim.y) {
             int h = e / a.dv, j = e % a.dv;
             CeType<T>::store((T*)a.v_pool + (((size_t)page * a.nkv + h) * a.page_size + off) * a.dv + j, row[a.off_v + e]);
         }
@@ -145,11 +146,16 @@ extern "C" int ce_norm_rope_kvwrite(const float* proj, void* q_out, void* k_pool
     NormRopeArgs a{proj, q_out, k_pool, v_pool, wq, wk, head_scale, rd > 0 ? cos_table : nullptr, sin_table, positions, seq_of_token,
                    seq_slot, block_table, status, ld, off_q, off_k, off_v, nh, nkv, d, dv, rd, page_size, max_pages, num_pages, max_pos,
                    write_kv, eps};
+    // a token's heads are dealt to the warps of gridDim.y blocks in turn: one block a token in a long step, a block per
+    // handful of heads in a step of few tokens
     int heads = nh + nkv;
     int threads = heads >= 8 ? 256 : 32 * heads;
+    int per_block = threads / 32, want = (heads + per_block - 1) / per_block, room = 4 * 148 / T;
+    int split = want < room ? want : room;
+    dim3 grid(T, split < 1 ? 1 : split);
     ce_note("norm_rope_kvwrite_kernel");
-    if (dtype == CE_F32) ce_launch(norm_rope_kvwrite_kernel<float>, T, threads, 0, stream, a);
-    else if (dtype == CE_BF16) ce_launch(norm_rope_kvwrite_kernel<__nv_bfloat16>, T, threads, 0, stream, a);
+    if (dtype == CE_F32) ce_launch(norm_rope_kvwrite_kernel<float>, grid, threads, 0, stream, a);
+    else if (dtype == CE_BF16) ce_launch(norm_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, 0, stream, a);
     else return ce_fail(CE_ERR_ARG, "ce_norm_rope_kvwrite: unknown dtype %d", dtype);
     return ce_check_launch("ce_norm_rope_kvwrite");
 }
