@@ -4,7 +4,8 @@ config.json names the design with ``"architecture": "Pugozen"`` and describes th
 
 * ``vocab``, ``width``: vocabulary and residual width; ``embedding`` = ``{"scale"}`` multiplies the embedding rows;
 * ``layers``: a list of ``{"type", "mixer", "mlp"}`` and optionally ``"weights_of": j`` (the layer has no tensors of its own
-  and runs layer j's, with a cache of its own).  ``type`` is
+  and runs layer j's, with a cache of its own; sizes and constants are then layer j's).  ``kv_heads`` left out means as
+  many as ``heads``.  ``type`` is
   ``"retention"`` (linear attention with a fixed decay per head: ``heads``, ``dim``, ``vdim``, ``decay`` = one number per
   head, ``rot`` = ``{"dims", "base"}``),
   ``"delta"`` (the gated delta rule with one decay per head: ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` taps) or
@@ -60,6 +61,7 @@ def _rot(m: Dict[str, Any], where: str) -> None:
 def _delta(m: Any, where: str, ranks: bool) -> None:
     if not isinstance(m, dict):
         raise ConfigError(f"config.json: {where}an object is expected")
+    m.setdefault("kv_heads", m.get("heads"))
     heads, kv = _int(m, "heads", where), _int(m, "kv_heads", where)
     if heads % kv:
         raise ConfigError(f"config.json: {where}{heads} heads are not a multiple of {kv} kv_heads")
@@ -74,6 +76,7 @@ def _check_layer(i: int, layer: Any) -> Dict[str, Any]:
     where = f"layers[{i}]: "
     if not isinstance(layer, dict) or not isinstance(layer.get("mixer"), dict):
         raise ConfigError(f"config.json: {where}an object with 'type', 'mixer' and 'mlp' is expected")
+    layer = copy.deepcopy(layer)
     kind, m = layer.get("type"), layer["mixer"]
     if kind == RETENTION:
         heads = _int(m, "heads", where)
@@ -89,6 +92,7 @@ def _check_layer(i: int, layer: Any) -> Dict[str, Any]:
         left = m.get("left")
         if not isinstance(left, dict):
             raise ConfigError(f"config.json: {where}'left' must be an object")
+        left.setdefault("kv_heads", left.get("heads"))
         heads, kv = _int(left, "heads", where + "left: "), _int(left, "kv_heads", where + "left: ")
         if heads % kv:
             raise ConfigError(f"config.json: {where}left: {heads} heads are not a multiple of {kv} kv_heads")
@@ -106,7 +110,7 @@ def _check_layer(i: int, layer: Any) -> Dict[str, Any]:
         if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
             raise ConfigError(f"config.json: {where}mlp must be null or of kind 'dense', got {mlp!r}")
         _int(mlp, "ff", where + "mlp: ")
-    out = {"type": kind, "mixer": copy.deepcopy(m), "mlp": copy.deepcopy(mlp)}
+    out = {"type": kind, "mixer": m, "mlp": mlp}
     if layer.get("weights_of") is not None:
         out["weights_of"] = _int(layer, "weights_of", where, 0)
     return out
@@ -143,9 +147,8 @@ class PugozenConfig(ModelConfig):
                 continue
             if j >= len(checked) or j == i:
                 raise ConfigError(f"config.json: layers[{i}]: 'weights_of' must name another layer, got {j}")
-            owner = checked[weight_owner(checked, i)]
-            if owner["type"] != layer["type"] or owner["mixer"] != layer["mixer"] or owner["mlp"] != layer["mlp"]:
-                raise ConfigError(f"config.json: layers[{i}] runs layer {j}'s weights but describes another layer")
+            weight_owner(checked, i)           # refuses a circle
+            # the layer's own entry is taken to equal its owner's: sizes and constants are the owner's, whose tensors it runs
         norm = raw.get("norm")
         if not isinstance(norm, dict):
             raise ConfigError("config.json: 'norm' must be an object with 'eps'")

@@ -215,7 +215,7 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
 // NEXT token are read, and k * decay formed, while the current token's sums travel over the lanes; the decayed state
 // decay * S is formed beside the dot product (k * decay)^T S of the old state instead of before it; the read-out q^T S is
 // off the chain altogether.
-template <int RPT, bool VEC, int GD_R>
+template <int RPT, bool VEC, int GD_R, bool DELTA>
 __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a, int n_buf) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float gd_smem[];
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
     if (t_end <= t_begin) return;
     int ncols = min(GD_COLS, dv - col0);
-    const bool delta = a.rule == 0;
+    constexpr bool delta = DELTA;              // false: the plain sum of outer products, whose write needs no dot product
     int jj = tid / GD_R, g = tid % GD_R, j = col0 + jj;
     bool owner = jj < ncols;
     float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * dv;
@@ -293,8 +293,10 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
 #pragma unroll
                 for (int m = 0; m < R4; ++m) {
                     float2 s01 = make_float2(S[4 * m], S[4 * m + 1]), s23 = make_float2(S[4 * m + 2], S[4 * m + 3]);
-                    p01 = __ffma2_rn(lo2(kw[m]), s01, p01);
-                    p23 = __ffma2_rn(hi2(kw[m]), s23, p23);
+                    if (delta) {
+                        p01 = __ffma2_rn(lo2(kw[m]), s01, p01);
+                        p23 = __ffma2_rn(hi2(kw[m]), s23, p23);
+                    }
                     dS[2 * m] = __fmul2_rn(lo2(w[m]), s01);
                     dS[2 * m + 1] = __fmul2_rn(hi2(w[m]), s23);
                     kc[m] = k[m]; qc[m] = q[m];
@@ -375,12 +377,16 @@ static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, int n_buf, 
     size_t smem = (size_t)n_buf * ((floats + 3) / 4 * 4) * sizeof(float);
     dim3 grid(a.H, B, (a.dv + GD_COLS - 1) / GD_COLS);
     ce_note("gated_delta_walk_kernel");
-    if (vec) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, true, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, true, R>, grid, R * GD_COLS, smem, stream, a, n_buf);
+    auto go = [&](auto kernel) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(kernel, grid, R * GD_COLS, smem, stream, a, n_buf);
+    };
+    if (a.rule == 0) {
+        if (vec) go(gated_delta_walk_kernel<RPT, true, R, true>);
+        else go(gated_delta_walk_kernel<RPT, false, R, true>);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, false, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, false, R>, grid, R * GD_COLS, smem, stream, a, n_buf);
+        if (vec) go(gated_delta_walk_kernel<RPT, true, R, false>);
+        else go(gated_delta_walk_kernel<RPT, false, R, false>);
     }
 }
 

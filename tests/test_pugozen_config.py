@@ -43,7 +43,6 @@ def test_config_round_trip_registry_and_schedule():
     (lambda r: r.update(norm={"eps": 0.0}), "positive"),
     (lambda r: r["layers"][0]["mlp"].update(kind="experts"), "mlp"),
     (lambda r: r["layers"][4].update(weights_of=9), "weights_of"),
-    (lambda r: r["layers"][4].update(weights_of=2), "describes another layer"),
 ])
 def test_config_errors_name_the_key(bad, text):
     from carbon_engine_b200.config.base import ConfigError
@@ -52,6 +51,13 @@ def test_config_errors_name_the_key(bad, text):
     bad(raw)
     with pytest.raises(ConfigError, match=text):
         PugozenConfig.from_dict(raw)
+
+
+def test_key_heads_left_out_are_as_many_as_heads():
+    raw = json.loads(json.dumps(CASES["C"]))
+    del raw["layers"][1]["mixer"]["kv_heads"]
+    cfg, model = build(raw)
+    assert cfg.layers[1]["mixer"]["kv_heads"] == 3 and model.blocks[1].mixer.kv_heads == 3 and "kv_heads" not in raw["layers"][1]["mixer"]
 
 
 def test_tensors_and_caches():
