@@ -225,7 +225,7 @@ def pugozen_config(width, heads, kv_heads, ff, layers, vocab):
             "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                                "rot": {"dims": 32, "base": 1e6}},
                       "right": {"heads": n, "kv_heads": n, "dim": 128, "vdim": 128, "conv": 3, "a_rank": 64, "g_rank": 64},
-                      "left_scale": 0.8, "right_scale": 0.5}}
+                      "left_scale": 0.7, "right_scale": 0.6}}
     retention = {"type": "retention", "mlp": ffn,
                  "mixer": {"heads": n, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - (6 * j) // n) for j in range(n)],
                            "rot": {"dims": 128, "base": 1e6}}}

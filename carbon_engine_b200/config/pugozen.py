@@ -205,7 +205,7 @@ def sketch_config(vocab: int, width: int, n_layers: int, heads: int, kv_heads: i
                           "rot": {"dims": rot, "base": rope_base}},
                  "right": {"heads": state_heads, "kv_heads": state_heads, "dim": head_dim, "vdim": head_dim, "conv": 3,
                            "a_rank": max(8, width // 32 * 2), "g_rank": max(8, width // 32 * 2)},
-                 "left_scale": 0.75, "right_scale": 0.5}
+                 "left_scale": 0.7, "right_scale": 0.6}
         layer = {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff}}
         if shared_from > 0 and i >= shared_from:
             layer["weights_of"] = i - shared_from

@@ -30,7 +30,7 @@ def delta(heads=4, kv_heads=2, dim=8, vdim=12, conv=4, ff=None):
 
 
 def pair(heads=4, kv_heads=2, dim=16, rot_dims=6, base=200.0, scale=0.3, r_heads=2, r_kv_heads=1, r_dim=8, r_vdim=12, conv=3,
-         a_rank=5, g_rank=3, left_scale=0.8, right_scale=0.5, ff=None):
+         a_rank=5, g_rank=3, left_scale=0.7, right_scale=0.6, ff=None):
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale}
     if rot_dims:
         left["rot"] = {"dims": rot_dims, "base": base}
@@ -74,11 +74,11 @@ CASES: Dict[str, dict] = {
                 width=48, vocab=75, scale=1.0),
 }
 # Head sizes the tensor-core attention kernel takes (multiples of 16) and state heads of the sizes of a mid-sized model
-CASES["T"] = config([pair(heads=4, kv_heads=2, dim=64, rot_dims=16, scale=0.11, r_heads=2, r_kv_heads=2, r_dim=64, r_vdim=64, conv=3,
+CASES["T"] = config([pair(heads=6, kv_heads=2, dim=64, rot_dims=32, scale=0.11, r_heads=2, r_kv_heads=2, r_dim=64, r_vdim=48, conv=3,
                           a_rank=8, g_rank=8, ff=72),
-                     delta(heads=4, kv_heads=2, dim=32, vdim=32, conv=4, ff=96),
-                     retention(heads=2, dim=64, vdim=64, decay=(0.984375, 0.9990234375), rot_dims=64, base=1e6),
-                     shared(pair(heads=4, kv_heads=2, dim=64, rot_dims=16, scale=0.11, r_heads=2, r_kv_heads=2, r_dim=64, r_vdim=64,
+                     delta(heads=6, kv_heads=3, dim=32, vdim=48, conv=4, ff=96),
+                     retention(heads=2, dim=64, vdim=64, decay=(0.97, 0.9995), rot_dims=64, base=5e5),
+                     shared(pair(heads=6, kv_heads=2, dim=64, rot_dims=32, scale=0.11, r_heads=2, r_kv_heads=2, r_dim=64, r_vdim=48,
                                  conv=3, a_rank=8, g_rank=8, ff=72), 0)],
                     width=128, vocab=151)
 CASES["V"] = config([retention(heads=2, dim=128, vdim=64, decay=(0.99, 0.999), rot_dims=32, ff=256),
