@@ -70,6 +70,8 @@ struct MmaAttnArgs {
     int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, split, fused_merge;
     int cluster_merge;          // TMA decode kernel: the splits of a sequence form a cluster and merge through shared memory
     float scale_log2;           // scale * log2(e)
+    const float* sinks;         // [nh] or null: exp(sinks[h]) joins head h's denominator, with no key and no value
+    float out_scale;            // the stored rows are multiplied by this
 };
 
 // Stage keys [k0, k0 + AM_TILE) of one KV head into shared memory rows of d + AM_PAD elements.
@@ -368,7 +370,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
             L += __ldcg(&a.part_ml[(base + s) * 2 + 1]) * f;
         }
         for (int o2 = 16; o2 > 0; o2 >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o2);
-        float inv = L > 0.f ? 1.0f / L : 0.f;
+        float inv = ce_softmax_inverse(M, L, a.sinks, kvh * G + hg * 16 + r, a.out_scale);
         __syncwarp();
         for (int s = lane; s < ns; s += 32) wts[r * ns + s] *= inv;
     }
@@ -737,11 +739,11 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
                 w[sp] = (sp < ns && ms[sp] != -INFINITY) ? ce_exp2_fast(ms[sp] - M) : 0.f;
                 if (w[sp] != 0.f) L += amt_ld_cluster(amt_map(amt_smem(fl + r), sp)) * w[sp];
             }
-            float inv = L > 0.f ? 1.0f / L : 0.f;
+            int h = kvh * G + hg * 8 + r;
+            float inv = ce_softmax_inverse(M, L, a.sinks, h, a.out_scale);
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp)
                 if (w[sp] != 0.f) acc = fmaf(amt_ld_cluster(amt_map(amt_smem(so + r * d + col), sp)), w[sp] * inv, acc);
-            int h = kvh * G + hg * 8 + r;
             a.out[((size_t)t * a.nh + h) * d + col] = __float2bfloat16_rn(acc);
         }
     }
@@ -775,7 +777,7 @@ __global__ void attention_merge_kernel(MmaAttnArgs a) {
             L += a.part_ml[(base + s) * 2 + 1] * f;
         }
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-        float inv = L > 0.f ? 1.0f / L : 0.f;
+        float inv = ce_softmax_inverse(M, L, a.sinks, h, a.out_scale);
         __syncwarp();
         for (int s = lane; s < ns; s += 32) wts[s] *= inv;
     }
@@ -871,7 +873,7 @@ __global__ void __launch_bounds__(AM_THREADS, DMAX <= 128 ? 3 : 1) attention_pre
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
-    float inv0 = l[0] > 0.f ? 1.0f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.0f / l[1] : 0.f;
+    float inv0 = ce_softmax_inverse(m[0], l[0], a.sinks, h, a.out_scale), inv1 = ce_softmax_inverse(m[1], l[1], a.sinks, h, a.out_scale);
     bf16* oa = a.out + ((size_t)(t0 + q0 + r0) * a.nh + h) * d;
     bf16* ob = a.out + ((size_t)(t0 + q0 + r1) * a.nh + h) * d;
 #pragma unroll
@@ -920,11 +922,30 @@ extern "C" int ce_attention_decode_tma_supported(int d, int page_size) {
     return d >= 64 && d <= 256 && d % 64 == 0 && page_size >= 8 && (page_size & (page_size - 1)) == 0;
 }
 
+// ``sinks`` (float32 [nh] or null) and ``out_scale``: see ce_softmax_inverse.
+extern "C" int ce_attention_decode_bf16_sink(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                                             int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
+                                             const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
+                                             int nkv, int d, int q_stride, int page_size, int max_pages, int num_pages,
+                                             int window, float scale, int max_splits, const float* sinks, float out_scale,
+                                             cudaStream_t stream);
+
 extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                                         int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
                                         const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
                                         int nkv, int d, int q_stride, int page_size, int max_pages, int num_pages,
                                         int window, float scale, int max_splits, cudaStream_t stream) {
+    return ce_attention_decode_bf16_sink(q, k_pool, v_pool, out, scratch, counters, n_counters, positions, seq_slot, q_start, ctx_len,
+                                         block_table, status, n_seqs, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window,
+                                         scale, max_splits, nullptr, 1.0f, stream);
+}
+
+extern "C" int ce_attention_decode_bf16_sink(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                                             int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
+                                             const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
+                                             int nkv, int d, int q_stride, int page_size, int max_pages, int num_pages,
+                                             int window, float scale, int max_splits, const float* sinks, float out_scale,
+                                             cudaStream_t stream) {
     if (n_seqs == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !scratch || !counters || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !status)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: null pointer");
@@ -939,6 +960,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     a.status = status; a.nh = nh; a.nkv = nkv; a.d = d; a.q_stride = q_stride; a.page_size = page_size;
     a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.sinks = sinks; a.out_scale = out_scale;
     int G = nh / nkv;
     static int use_tma = getenv("CE_ATTN_NO_TMA") ? 0 : 1;
     static int fused = getenv("CE_ATTN_FUSED_MERGE") ? 1 : 0;
@@ -1067,11 +1089,29 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
 
 // tiles: [n_tiles, 2] = (sequence, first new token of the tile); tiles cover the sequences that
 // bring more than one token, 64 tokens at a time.
+extern "C" int ce_attention_prefill_bf16_sink(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                              const int* positions, const int* seq_slot, const int* q_start,
+                                              const int* ctx_len, const int* block_table, const int* tiles, int* status,
+                                              int n_tiles, int nh, int nkv, int d, int q_stride, int page_size,
+                                              int max_pages, int num_pages, int window, float scale, const float* sinks,
+                                              float out_scale, cudaStream_t stream);
+
 extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                          const int* positions, const int* seq_slot, const int* q_start,
                                          const int* ctx_len, const int* block_table, const int* tiles, int* status,
                                          int n_tiles, int nh, int nkv, int d, int q_stride, int page_size,
                                          int max_pages, int num_pages, int window, float scale, cudaStream_t stream) {
+    return ce_attention_prefill_bf16_sink(q, k_pool, v_pool, out, positions, seq_slot, q_start, ctx_len, block_table, tiles, status,
+                                          n_tiles, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, nullptr, 1.0f,
+                                          stream);
+}
+
+extern "C" int ce_attention_prefill_bf16_sink(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                              const int* positions, const int* seq_slot, const int* q_start,
+                                              const int* ctx_len, const int* block_table, const int* tiles, int* status,
+                                              int n_tiles, int nh, int nkv, int d, int q_stride, int page_size,
+                                              int max_pages, int num_pages, int window, float scale, const float* sinks,
+                                              float out_scale, cudaStream_t stream) {
     if (n_tiles == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !tiles || !status)
         return ce_fail(CE_ERR_ARG, "ce_attention_prefill_bf16: null pointer");
@@ -1084,6 +1124,7 @@ extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, cons
     a.tiles = tiles; a.status = status; a.nh = nh; a.nkv = nkv; a.d = d; a.q_stride = q_stride; a.page_size = page_size;
     a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.sinks = sinks; a.out_scale = out_scale;
     dim3 grid(n_tiles, nh);
     size_t smem = stage_bytes(d, AM_PF_STAGES);
     if (d <= 64) {

@@ -146,6 +146,8 @@ struct TcAttnArgs {
     int* status;
     int nh, nkv, page_size, page_shift, max_pages, num_pages, window;
     float scale_log2;
+    const float* sinks;         // [nh] or null: exp(sinks[h]) joins head h's denominator, with no key and no value
+    float out_scale;            // the stored rows are multiplied by this
 };
 
 template <int D>
@@ -417,7 +419,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             // tensor-memory loads are warp-wide: every lane takes part, only real query rows store
-            float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            float inv = ce_softmax_inverse(m_run, l_run, a.sinks, h, a.out_scale);
             __nv_bfloat16* orow = a.out + ((size_t)(t0 + q0 + row) * a.nh + h) * D;
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
@@ -469,11 +471,28 @@ extern "C" int ce_attention_prefill_tc_supported(int d, int page_size, int q_str
 
 // tiles: [n_tiles, 2] = (sequence, first new token of the tile), 128 tokens a tile, over the
 // sequences that bring more than one token.  total_tokens: rows of q.
+extern "C" int ce_attention_prefill_tc_sink(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_slot,
+                                            const int* q_start, const int* ctx_len, const int* block_table, const int* tiles,
+                                            int* status, int n_tiles, int total_tokens, int nh, int nkv, int d, int q_stride,
+                                            int page_size, int max_pages, int num_pages, int window, float scale,
+                                            const float* sinks, float out_scale, cudaStream_t stream);
+
 extern "C" int ce_attention_prefill_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_slot,
                                        const int* q_start, const int* ctx_len, const int* block_table, const int* tiles,
                                        int* status, int n_tiles, int total_tokens, int nh, int nkv, int d, int q_stride,
                                        int page_size, int max_pages, int num_pages, int window, float scale,
                                        cudaStream_t stream) {
+    return ce_attention_prefill_tc_sink(q, k_pool, v_pool, out, seq_slot, q_start, ctx_len, block_table, tiles, status, n_tiles,
+                                        total_tokens, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, nullptr,
+                                        1.0f, stream);
+}
+
+// ``sinks`` (float32 [nh] or null) and ``out_scale``: see ce_softmax_inverse.
+extern "C" int ce_attention_prefill_tc_sink(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_slot,
+                                            const int* q_start, const int* ctx_len, const int* block_table, const int* tiles,
+                                            int* status, int n_tiles, int total_tokens, int nh, int nkv, int d, int q_stride,
+                                            int page_size, int max_pages, int num_pages, int window, float scale,
+                                            const float* sinks, float out_scale, cudaStream_t stream) {
     if (n_tiles == 0) return CE_OK;
     if (!q || !k_pool || !v_pool || !out || !seq_slot || !q_start || !ctx_len || !block_table || !tiles || !status)
         return ce_fail(CE_ERR_ARG, "ce_attention_prefill_tc: null pointer");
@@ -492,7 +511,7 @@ extern "C" int ce_attention_prefill_tc(const void* q, const void* k_pool, const 
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
     TcAttnArgs a{(__nv_bfloat16*)out, seq_slot, q_start, ctx_len, block_table, tiles, status, nh, nkv, page_size, shift,
-                 max_pages, num_pages, window, scale * 1.4426950408889634f};
+                 max_pages, num_pages, window, scale * 1.4426950408889634f, sinks, out_scale};
     if (n_tiles > 65535) return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: %d tiles of 128 tokens in one step", n_tiles);
     dim3 grid(nh, n_tiles);
     return d == 64 ? launch<64>(mq, mk, mv, a, grid, stream) : launch<128>(mq, mk, mv, a, grid, stream);

@@ -54,6 +54,19 @@ int ce_sm_count();
 // 2^x in one MUFU instruction (relative error about 2^-22; -inf gives 0).  exp2f() costs several
 // instructions around the same MUFU; the bfloat16 attention kernels, whose probabilities are rounded to
 // 8 bits of mantissa anyway, are bound by exactly those instructions.
+// What a softmax row's sums are divided by, as its inverse.  M: the row's running maximum, L: its sum of 2^(s - M), both in
+// the base-2 domain.  ``sinks`` (or null): a learned number per head whose exponential is one more term of the denominator,
+// with no key and no value (given in the natural domain; it is neither scaled nor masked).  ``out_scale`` multiplies the result.
+__device__ __forceinline__ float ce_softmax_inverse(float M, float L, const float* sinks, int h, float out_scale) {
+    float shrink = 1.0f;
+    if (sinks) {
+        float sk = sinks[h] * 1.4426950408889634f, big = fmaxf(M, sk);
+        shrink = M == -INFINITY ? 0.f : exp2f(M - big);
+        L = L * shrink + exp2f(sk - big);
+    }
+    return (L > 0.f ? shrink / L : 0.f) * out_scale;
+}
+
 __device__ __forceinline__ float ce_exp2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

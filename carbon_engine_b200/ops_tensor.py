@@ -15,11 +15,14 @@ kernel_lib.declare("ce_attention_decode_scratch", _ll, [_i, _i, _i, _i])
 # q, k_pool, v_pool, out, scratch, counters, n_counters, positions, seq_slot, q_start, ctx_len, block_table, status,
 # n_seqs, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, max_splits, stream
 kernel_lib.declare("ce_attention_decode_bf16", _i, [_p] * 6 + [_i] + [_p] * 6 + [_i] * 9 + [_f, _i, _p])
+# the same with, before the stream: sinks (float32 [nh] or null), out_scale
+kernel_lib.declare("ce_attention_decode_bf16_sink", _i, [_p] * 6 + [_i] + [_p] * 6 + [_i] * 9 + [_f, _i, _p, _f, _p])
 kernel_lib.declare("ce_attention_decode_split", _i, [])
 kernel_lib.declare("ce_attention_decode_kernels", _i, [])
 # q, k_pool, v_pool, out, positions, seq_slot, q_start, ctx_len, block_table, tiles, status,
 # n_tiles, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
 kernel_lib.declare("ce_attention_prefill_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _p])
+kernel_lib.declare("ce_attention_prefill_bf16_sink", _i, [_p] * 11 + [_i] * 9 + [_f, _p, _f, _p])
 
 kernel_lib.declare("ce_gemm_tc_supported", _i, [_i, _i, _i, _i])
 kernel_lib.declare("ce_gemm_tc_scratch", _ll, [_i, _i, _i, _i])
@@ -42,6 +45,7 @@ kernel_lib.declare("ce_attention_prefill_tc_supported", _i, [_i, _i, _i])
 # q, k_pool, v_pool, out, seq_slot, q_start, ctx_len, block_table, tiles, status,
 # n_tiles, total_tokens, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
 kernel_lib.declare("ce_attention_prefill_tc", _i, [_p] * 10 + [_i] * 10 + [_f, _p])
+kernel_lib.declare("ce_attention_prefill_tc_sink", _i, [_p] * 10 + [_i] * 10 + [_f, _p, _f, _p])
 
 #: set to False to keep portions of prompts off the tcgen05 attention kernel (the mma.sync one takes them)
 USE_TENSOR_ATTENTION = True
@@ -143,34 +147,39 @@ def attention_supported(d: int, q_stride: int) -> bool:
     return 16 <= d <= 256 and d % 16 == 0 and q_stride % 2 == 0
 
 
-def attention_bf16(ctx, plan, qkv, out, cache, table, nh, nkv, d, window, scale) -> bool:
+def attention_bf16(ctx, plan, qkv, out, cache, table, nh, nkv, d, window, scale, sinks=None, out_scale: float = 1.0) -> bool:
     """Decode kernel for the leading one-token sequences, flash kernel for the portions.  ``plan``: the
-    step's tile lists and split bound (``parts.attention.AttentionPlan``)."""
+    step's tile lists and split bound (``parts.attention.AttentionPlan``).  ``qkv``: rows whose leading ``nh * d``
+    columns are the query heads.  ``sinks`` (float32 [nh] or None): a number per head whose exponential joins the
+    softmax's denominator without a key or a value; ``out_scale`` multiplies what is stored."""
     if not attention_supported(d, qkv.shape[1]):
         return False
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh or not sinks.is_cuda or not sinks.is_contiguous()):
+        raise ops.KernelError(f"attention sinks must be {nh} float32 numbers on the GPU")
     k = kernels()
     stream = ops._stream()
     args = (cache.page_size, table.shape[1], cache.k_pool.shape[0], int(window), float(scale))
+    tail = (None if sinks is None else sinks.data_ptr(), float(out_scale), stream)
     if ctx.n_decode > 0:
         splits = plan.decode_splits
         need = k.ce_attention_decode_scratch(ctx.n_decode, nh, d, splits)
         scratch = ctx.scratch("attention_decode", need)
         ws = gemm_workspace(qkv.device)
-        ops._ok(k.ce_attention_decode_bf16(
+        ops._ok(k.ce_attention_decode_bf16_sink(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), scratch.data_ptr(),
             ws.attn_counters.data_ptr(), ws.attn_counters.numel(), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
-            table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream),
+            table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, *tail),
                 k.ce_attention_decode_kernels())
     if plan.n_tiles > 0 and USE_TENSOR_ATTENTION and plan.n_tiles128 > 0 and \
             k.ce_attention_prefill_tc_supported(d, cache.page_size, qkv.shape[1]):
-        ops._ok(k.ce_attention_prefill_tc(
+        ops._ok(k.ce_attention_prefill_tc_sink(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), ctx.seq_slot.data_ptr(),
             ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(), table.data_ptr(), plan.tiles128.data_ptr(),
-            ctx.status.data_ptr(), plan.n_tiles128, qkv.shape[0], nh, nkv, d, qkv.shape[1], *args, stream))
+            ctx.status.data_ptr(), plan.n_tiles128, qkv.shape[0], nh, nkv, d, qkv.shape[1], *args, *tail))
     elif plan.n_tiles > 0:
-        ops._ok(k.ce_attention_prefill_bf16(
+        ops._ok(k.ce_attention_prefill_bf16_sink(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(),
             ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
             table.data_ptr(), plan.tiles.data_ptr(), ctx.status.data_ptr(), plan.n_tiles, nh, nkv, d, qkv.shape[1],
-            *args, stream))
+            *args, *tail))
     return True

@@ -10,8 +10,11 @@ exp(sink_h) (``sink``: a stored number per head that has no key and no value and
 temperature); the heads' weighted sums of the values; the output product.  With ``tied_values`` the values are the key
 projection's output itself, before the norm and the rotation, so the value size is ``dim`` and there is no ``.v`` tensor.
 
-The attention runs on the masked-attention family's kernels (``parts/masked_attention.py:attend``).  ``out_scale``
-multiplies the heads' outputs before the output product (the mixer's weight where mixers are summed).
+Where values and keys have one size, bfloat16 steps run the kernels of :class:`carbon_engine_b200.parts.attention.PagedAttention`
+(the split-KV decode kernel fed by TMA and the tcgen05 flash kernel, which take the sink and the output's factor at the point
+where a row's sums are inverted); float32 steps, other head sizes and values of another size run the masked-attention family's
+kernels (``parts/masked_attention.py:attend``).  ``out_scale`` multiplies the heads' outputs before the output product (the
+mixer's weight where mixers are summed).
 """
 from __future__ import annotations
 
@@ -23,6 +26,7 @@ import torch
 from .. import ops
 from .base import Mixer, PagedCacheSpec, Part, TensorGetter, TensorSpec, register_init_kind
 from .linear import ACCUM, STORE_F32, Linear
+from .attention import PagedAttention
 from .masked_attention import attend, plan_query_tiles
 from .rope import PositionEncoding
 
@@ -33,8 +37,7 @@ register_init_kind("temperature", 1.0, 0.2, True)
 class SinkAttention(Mixer):
     graph_safe = True
     can_store = True
-    plan_key = "masked_attention"
-    TILE = 64               # query tokens a block of the tensor-core kernel takes
+    TILE, TILE_TC = PagedAttention.TILE, PagedAttention.TILE_TC       # tokens per tile of the flash kernels
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, prefix: str, eps: float, vdim: Optional[int] = None,
                  position: Optional[PositionEncoding] = None, scale: Optional[float] = None, window: int = 0, qk_norm: bool = True,
@@ -52,6 +55,8 @@ class SinkAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(dim)
         self.qk_norm, self.tied_values, self.head_temperature, self.sink = bool(qk_norm), bool(tied_values), bool(head_temperature), bool(sink)
         self.out_scale, self.page_size = float(out_scale), page_size
+        # values of the keys' size: the step is planned for, and runs on, the paged attention's kernels
+        self.plan_key = PagedAttention.plan_key if vdim == dim else "masked_attention"
         p = prefix
         sizes, names = [heads * dim, kv_heads * dim], [f"{p}.q", f"{p}.k"]
         if not tied_values:
@@ -92,10 +97,14 @@ class SinkAttention(Mixer):
         return tokens * (self.qkv.padded_out * 4 + self.heads * (self.dim + self.vdim) * element_size)
 
     def step_sections(self, max_tokens: int, max_seqs: int):
-        return [("masked_attention.tiles", 2 * (max_seqs + max_tokens // self.TILE + 1))]
+        if self.plan_key == PagedAttention.plan_key:
+            return PagedAttention.step_sections(self, max_tokens, max_seqs)
+        return [("masked_attention.tiles", 2 * (max_seqs + max_tokens // 64 + 1))]
 
     def plan_step(self, ctx):
-        return plan_query_tiles(ctx, "masked_attention.tiles", self.TILE)
+        if self.plan_key == PagedAttention.plan_key:
+            return PagedAttention.plan_step(self, ctx)
+        return plan_query_tiles(ctx, "masked_attention.tiles", 64)
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache, accumulate: bool = True) -> None:
         T = h.shape[0]
@@ -115,6 +124,22 @@ class SinkAttention(Mixer):
                               0, off_k, off_v, H, G, d, dv, pos.rotary_dim if cos is not None else 0, cache.page_size, self.eps,
                               write_kv=cache.writes)
         out = ctx.buffer((T, H * dv))
-        attend(ctx, ctx.plans.get(self.plan_key), q, d, cache, d, dv, cache.v_pool, None, out, table, H, G, d, dv, self.window, 0,
+        plan = ctx.plans.get(self.plan_key)
+        fast = self.plan_key == PagedAttention.plan_key
+        if fast and q.dtype == torch.bfloat16 and ctx.fast_attention and plan is not None:
+            from .. import ops_tensor
+            prof = ops.profiling()
+            if prof is not None:         # keys and values of every sequence once, queries and outputs; causal flops
+                keys = pairs = 0
+                for b in range(ctx.B):
+                    n, before = ctx.h_q_start[b + 1] - ctx.h_q_start[b], ctx.h_ctx_before[b]
+                    keys += before + n
+                    pairs += n * before + n * (n + 1) // 2
+                prof.note_work((2 * keys * G * d + 2 * ctx.T * H * d) * 2, 4 * pairs * H * d)
+            if ops_tensor.attention_bf16(ctx, plan, q, out, cache, table, H, G, d, self.window, self.scale, sinks=self.sinks,
+                                         out_scale=self.out_scale):
+                self.o.forward(out, x, ACCUM if accumulate else STORE_F32)
+                return
+        attend(ctx, None if fast else plan, q, d, cache, d, dv, cache.v_pool, None, out, table, H, G, d, dv, self.window, 0,
                self.scale, 0.0, sinks=self.sinks, out_scale=self.out_scale)
         self.o.forward(out, x, ACCUM if accumulate else STORE_F32)

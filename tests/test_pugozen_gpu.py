@@ -213,14 +213,17 @@ def test_whole_prompt_portions_and_decoding(tmp_path, name, dtype):
     h = Harness(folder, dtype, page_size=8, pages=24)          # 192 tokens of pages: every run reuses the last one's
     ops.reset_kernel_counts()
     whole = h.run(toks)
-    if name in ("T", "V"):        # head sizes of the tensor-core kernel: bfloat16 must have taken it, float32 never
-        assert ("masked_attention_mma_kernel" in ops.kernel_counts()) == (dtype == "bfloat16")
+    if name in ("T", "V"):        # head sizes of the tensor-core kernels: bfloat16 must have taken them, float32 never
+        flash = "attention_prefill_tc_kernel" if name == "T" else "attention_prefill_kernel"       # heads of 64 / of 32
+        assert (flash in ops.kernel_counts()) == (dtype == "bfloat16")
     assert rel_err(whole, want) < TOL[dtype], "whole"
     for cuts in ([1], [2], [3, 2, 7, 2, 16, 5], [40, 1, 1, 1], [64, 19]):
         got = h.run(toks, cuts)
         assert rel_err(got, want) < TOL[dtype], cuts
         if dtype == "float32":
             assert np.array_equal(got, whole), cuts
+    if name == "T" and dtype == "bfloat16":          # single tokens: the split-KV kernel fed by TMA, merged inside a cluster
+        assert any(k.startswith("attention_decode_tma_kernel") for k in ops.kernel_counts())
     m = h.storage.manager
     assert all(m.free_pages(g) == h.storage.groups[g].num_pages for g in range(len(h.storage.groups))) and m.free_slots() == 4
 
@@ -272,14 +275,14 @@ def test_unequal_requests_in_one_batch_with_reused_pages_and_slots(tmp_path, dty
 
 
 # ---- a key that stands out, far away and at page borders; the sink ------------------------------------------------
-def standout_model(tmp_path, tag, sink=None, heads=2, kv_heads=1, d=16, rot_dims=6):
+def standout_model(tmp_path, tag, sink=None, heads=2, kv_heads=1, d=16, rot_dims=6, scale=2.0):
     """One pair layer whose attention makes EVERY query score the marker token's key far above hundreds of others.  The
     first embedding element is the same large number for every token, so the first normed element is nearly constant; one
     query element (past the rotated ones) reads it, and the same key element reads the direction of the marker's embedding:
     after the keys' norm (which a constant key element keeps alike for all tokens) it is large for the marker and noise for all others.  The delta rule beside it counts for nothing."""
     from helpers import read_raw_safetensors, write_safetensors_plain
     W, j = 32, 10
-    raw = config([pair(heads=heads, kv_heads=kv_heads, dim=d, rot_dims=rot_dims, scale=2.0, left_scale=1.0, right_scale=0.0)],
+    raw = config([pair(heads=heads, kv_heads=kv_heads, dim=d, rot_dims=rot_dims, scale=scale, left_scale=1.0, right_scale=0.0)],
                  width=W, vocab=50, scale=1.0)
     folder = write_model(raw, str(tmp_path / f"standout_{tag}"), seed=21)
     path = os.path.join(folder, "model.safetensors")
@@ -317,9 +320,17 @@ def marker_effect(folder, toks, at):
     return want, np.abs(want - plain_logits(folder, other)).max(axis=1) / np.abs(want).max()
 
 
+#: key sizes of the standout models with the scale that keeps the marker's score near 14: heads of 16 (in bfloat16 the
+#: mma.sync flash kernel and the cp.async decode kernel) and of 64 (the tcgen05 flash kernel and the TMA decode kernel)
+STANDOUT_HEADS = {16: 2.0, 64: 0.5}
+
+
+@pytest.mark.parametrize("d", sorted(STANDOUT_HEADS))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_far_key_among_hundreds_and_at_page_borders(tmp_path, dtype):
-    folder, raw = standout_model(tmp_path, "far")
+def test_a_far_key_among_hundreds_and_at_page_borders(tmp_path, dtype, d):
+    from carbon_engine_b200 import ops
+    folder, raw = standout_model(tmp_path, "far", d=d, scale=STANDOUT_HEADS[d])
+    ops.reset_kernel_counts()
     rng = np.random.default_rng(6)
     base = [int(t) for t in rng.integers(10, 50, 720)]
     h = Harness(folder, dtype, page_size=16, pages=48, max_step_tokens=1024)
@@ -335,23 +346,28 @@ def test_a_far_key_among_hundreds_and_at_page_borders(tmp_path, dtype):
             rows.append(h.step([(rid, toks[p:p + 1], [0])]))
         h.close(rid)
         assert rel_err(np.concatenate(rows), want[689:]) < TOL[dtype], marker_at
+    if dtype == "bfloat16":
+        ran = ops.kernel_counts()
+        assert ("attention_prefill_tc_kernel" if d == 64 else "attention_prefill_kernel") in ran
+        assert any(k.startswith("attention_decode_tma_kernel" if d == 64 else "attention_decode_kernel") for k in ran)
 
 
+@pytest.mark.parametrize("d", sorted(STANDOUT_HEADS))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_the_sink_takes_its_share_of_every_head(tmp_path, dtype):
+def test_the_sink_takes_its_share_of_every_head(tmp_path, dtype, d):
     """A sink about as large as the marker's score takes much of the marker's weight in one head and leaves the other alone; a model
     that left the sink out, scaled it or gave it the head's temperature would differ visibly."""
-    folder, raw = standout_model(tmp_path, "sink", sink=[13.0, -3.0])           # about the marker's score in head 0
-    no_sink, _ = standout_model(tmp_path, "nosink", sink=[-30.0, -30.0])
+    folder, raw = standout_model(tmp_path, "sink", sink=[13.0, -3.0], d=d, scale=STANDOUT_HEADS[d])     # about the marker's score in head 0
+    no_sink, _ = standout_model(tmp_path, "nosink", sink=[-30.0, -30.0], d=d, scale=STANDOUT_HEADS[d])
     rng = np.random.default_rng(2)
-    toks = [int(t) for t in rng.integers(10, 50, 90)]
+    toks = [int(t) for t in rng.integers(10, 50, 200)]
     toks[5] = 7
     want = plain_logits(folder, toks)
     assert rel_err(plain_logits(no_sink, toks), want) > 0.05            # the plain model itself: the sink matters
-    h = Harness(folder, dtype, page_size=8, pages=16)
+    h = Harness(folder, dtype, page_size=8, pages=32)
     whole = h.run(toks)
     assert rel_err(whole, want) < TOL[dtype]
-    for cuts in ([1], [2], [50, 3, 1]):
+    for cuts in ([1], [2], [150, 3, 1]):
         got = h.run(toks, cuts)
         assert rel_err(got, want) < TOL[dtype], cuts
         if dtype == "float32":
