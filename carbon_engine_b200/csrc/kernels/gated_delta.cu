@@ -345,6 +345,105 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     }
 }
 
+// A step of single tokens (every sequence brings exactly one): the walk's arithmetic for one token, laid out for bandwidth.
+// The state moves once, so what counts is how it is read and written: a block takes (head, sequence, 32 value channels), a warp
+// 32 neighbouring channels of the rows of one "lane" of the walk, so every load and store of the state is 128 contiguous bytes.
+// Thread (g, c) does exactly what lane g of column c does in the walk, term by term and in the same order; the two sums over
+// the lanes, which the walk takes with butterflies, are taken from shared memory in the butterflies' order (a balanced tree over
+// the lanes for the read-out; quads, then quads of quads, for the dot product).  A token therefore gets the same bits whether
+// it arrives alone or inside a portion.
+#define GD_STEP_COLS 32
+template <int RPT, int GD_R, bool DELTA>
+__global__ void __launch_bounds__(GD_R * GD_STEP_COLS) gated_delta_step_kernel(GatedDeltaArgs a) {
+    ce_pdl_begin();
+    constexpr int R4 = RPT / 4, dp = GD_R * RPT;
+    __shared__ __align__(16) float vec[3 * dp];                    // decay, key, query of the token, padded with zeros
+    __shared__ float dots[GD_R * GD_STEP_COLS], parts[GD_R * GD_STEP_COLS];
+    int d = a.d, dv = a.dv, H = a.H, G = a.G;
+    int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    int c = tid % GD_STEP_COLS, g = tid / GD_STEP_COLS, j = blockIdx.z * GD_STEP_COLS + c;
+    int t = a.q_start[b];
+    if (a.q_start[b + 1] <= t) return;
+    bool owner = j < dv;
+    int C = 2 * G * d + H * dv, kh = h / (H / G);
+    const float* row = a.prep + (size_t)t * a.P;
+    int offs[3] = {C + h * d, G * d + kh * d, kh * d};          // decay, key, query within a prep row
+    for (int e = tid; e < 3 * dp; e += blockDim.x) {
+        int which = e / dp, i = e % dp;
+        vec[e] = i < d ? row[offs[which] + i] : 0.f;
+    }
+    float* sp = a.state + ((size_t)a.seq_slot[b] * H + h) * d * dv;
+    float S[RPT];
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+        int r = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+        S[m] = (owner && r < d) ? sp[(size_t)r * dv + j] : 0.f;
+    }
+    float vj = owner ? row[2 * G * d + h * dv + j] : 0.f, beta = row[C + H * d + h];
+    __syncthreads();
+    float w[RPT], k[RPT], q[RPT], dS[RPT];
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+    for (int m4 = 0; m4 < R4; ++m4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(vec + 0 * dp + (m4 * GD_R + g) * 4);
+        const float4 k4 = *reinterpret_cast<const float4*>(vec + 1 * dp + (m4 * GD_R + g) * 4);
+        const float4 q4 = *reinterpret_cast<const float4*>(vec + 2 * dp + (m4 * GD_R + g) * 4);
+        w[4 * m4] = w4.x; w[4 * m4 + 1] = w4.y; w[4 * m4 + 2] = w4.z; w[4 * m4 + 3] = w4.w;
+        k[4 * m4] = k4.x; k[4 * m4 + 1] = k4.y; k[4 * m4 + 2] = k4.z; k[4 * m4 + 3] = k4.w;
+        q[4 * m4] = q4.x; q[4 * m4 + 1] = q4.y; q[4 * m4 + 2] = q4.z; q[4 * m4 + 3] = q4.w;
+        if (DELTA) {
+            p0 = fmaf(__fmul_rn(k[4 * m4], w[4 * m4]), S[4 * m4], p0);
+            p1 = fmaf(__fmul_rn(k[4 * m4 + 1], w[4 * m4 + 1]), S[4 * m4 + 1], p1);
+            p2 = fmaf(__fmul_rn(k[4 * m4 + 2], w[4 * m4 + 2]), S[4 * m4 + 2], p2);
+            p3 = fmaf(__fmul_rn(k[4 * m4 + 3], w[4 * m4 + 3]), S[4 * m4 + 3], p3);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dS[4 * m4 + i] = __fmul_rn(w[4 * m4 + i], S[4 * m4 + i]);
+    }
+    float u = vj;
+    if (DELTA) {
+        dots[g * GD_STEP_COLS + c] = __fadd_rn(__fadd_rn(p0, p1), __fadd_rn(p2, p3));
+        __syncthreads();
+        // the lanes' sums in the order of the walk's butterfly: quads of lanes, then quads of quads (then the two halves of 32)
+        float quad[GD_R / 4];
+#pragma unroll
+        for (int n = 0; n < GD_R / 4; ++n)
+            quad[n] = __fadd_rn(__fadd_rn(dots[(4 * n) * GD_STEP_COLS + c], dots[(4 * n + 1) * GD_STEP_COLS + c]),
+                                __fadd_rn(dots[(4 * n + 2) * GD_STEP_COLS + c], dots[(4 * n + 3) * GD_STEP_COLS + c]));
+        float dot = __fadd_rn(__fadd_rn(quad[0], quad[1]), __fadd_rn(quad[2], quad[3]));
+        if (GD_R == 32) dot = __fadd_rn(dot, __fadd_rn(__fadd_rn(quad[GD_R / 4 - 4], quad[GD_R / 4 - 3]), __fadd_rn(quad[GD_R / 4 - 2], quad[GD_R / 4 - 1])));
+        u = __fmul_rn(beta, __fsub_rn(vj, dot));
+    }
+    float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+#pragma unroll
+    for (int m4 = 0; m4 < R4; ++m4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) S[4 * m4 + i] = fmaf(k[4 * m4 + i], u, dS[4 * m4 + i]);
+        q0 = fmaf(S[4 * m4], q[4 * m4], q0);
+        q1 = fmaf(S[4 * m4 + 1], q[4 * m4 + 1], q1);
+        q2 = fmaf(S[4 * m4 + 2], q[4 * m4 + 2], q2);
+        q3 = fmaf(S[4 * m4 + 3], q[4 * m4 + 3], q3);
+    }
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+        int r = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+        if (owner && r < d) sp[(size_t)r * dv + j] = S[m];
+    }
+    parts[g * GD_STEP_COLS + c] = __fadd_rn(__fadd_rn(q0, q1), __fadd_rn(q2, q3));
+    __syncthreads();
+    if (g == 0 && owner) {
+        // a balanced tree over the lanes: neighbours, then pairs of pairs, and so on (the walk's butterfly with offsets 1, 2, 4, ...)
+        float tree[GD_R];
+#pragma unroll
+        for (int n = 0; n < GD_R; ++n) tree[n] = parts[n * GD_STEP_COLS + c];
+#pragma unroll
+        for (int o = 1; o < GD_R; o <<= 1)
+#pragma unroll
+            for (int n = 0; n < GD_R; n += 2 * o) tree[n] = __fadd_rn(tree[n], tree[n + o]);
+        a.raw[(size_t)t * H * dv + h * dv + j] = tree[0];
+    }
+}
+
 // A token's heads are dealt to the warps of gridDim.y blocks in turn: root mean square over the head's values, weight, gate.
 template <typename T>
 __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
@@ -450,6 +549,17 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
         // Measured at 2,048 tokens with heads of 128 x 128: 16 lanes a column took 0.63 ms (16 heads) and 0.90 ms (32 heads) a
         // launch, 32 lanes 0.61 and 1.21: twice the warps for the same columns, and with 32 heads the SMs' issue slots run out.
         int n_buf = T == B ? 1 : 2;             // as many tokens as sequences: every sequence brings exactly one
+        static int no_step = getenv("CE_DELTA_NO_STEP") ? 1 : 0;       // (for measurement: single tokens on the walk)
+        if (T == B && !no_step) {
+            dim3 grid(H, B, (dv + GD_STEP_COLS - 1) / GD_STEP_COLS);
+            ce_note("gated_delta_step_kernel");
+#define GD_STEP_CASE(RPT, R)                                                                                      \
+            if (a.rule == 0) ce_launch(gated_delta_step_kernel<RPT, R, true>, grid, R * GD_STEP_COLS, 0, stream, a);  \
+            else ce_launch(gated_delta_step_kernel<RPT, R, false>, grid, R * GD_STEP_COLS, 0, stream, a);
+            if (d <= 64) { GD_STEP_CASE(4, 16) } else if (d <= 128) { GD_STEP_CASE(8, 16) } else { GD_STEP_CASE(8, 32) }
+#undef GD_STEP_CASE
+            return ce_check_launch("ce_gated_delta");
+        }
         if (d <= 64) gd_launch_walk<4, 16>(a, B, vec, n_buf, stream);
         else if (d <= 128) gd_launch_walk<8, 16>(a, B, vec, n_buf, stream);
         else gd_launch_walk<8, 32>(a, B, vec, n_buf, stream);
