@@ -85,8 +85,9 @@ __global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
     if (a.operands == 1) {
         // no convolution: q and k rotated by the position, k scaled, v as it is
         const float* row = a.proj + (size_t)t * a.ld + a.off_conv;
-        int half = a.rd / 2, pos = a.positions[t];
+        int half = a.rd / 2;
         bool rotate = a.cos_table != nullptr && half > 0;
+        int pos = rotate ? a.positions[t] : 0;
         if (rotate && (pos < 0 || pos >= a.max_pos)) {
             if (thr == 0) atomicExch(a.status, 3);
             rotate = false;
@@ -179,8 +180,8 @@ __device__ __forceinline__ void gd_cp16(float* dst, const float* src) {
 }
 
 // Copies of one tile of tokens into a buffer: three vectors of d per token (decay, key, query; rows padded to DP floats),
-// GD_COLS values and beta.
-template <int DP, bool VEC>
+// BC values (the block's value channels) and beta.
+template <int DP, bool VEC, int BC>
 __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, int t0, int n_tok, int h, int col0, int ncols) {
     int d = a.d, G = a.G, H = a.H, tid = threadIdx.x, nthr = blockDim.x;
     int g = h / (H / G);
@@ -199,12 +200,12 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
             if (tok < n_tok && c < d) gd_cp4(buf + (which * GD_TILE + tok) * DP + c, a.prep + (size_t)(t0 + tok) * a.P + offs[which] + c);
         }
     }
-    for (int e = tid; e < GD_TILE * (GD_COLS + 1); e += nthr) {
-        int tok = e / (GD_COLS + 1), c = e % (GD_COLS + 1);
+    for (int e = tid; e < GD_TILE * (BC + 1); e += nthr) {
+        int tok = e / (BC + 1), c = e % (BC + 1);
         if (tok >= n_tok) continue;
         const float* row = a.prep + (size_t)(t0 + tok) * a.P;
-        if (c < ncols) gd_cp4(vbuf + tok * (GD_COLS + 1) + c, row + 2 * G * d + h * a.dv + col0 + c);
-        else if (c == GD_COLS) gd_cp4(vbuf + tok * (GD_COLS + 1) + c, row + C + H * d + h);
+        if (c < ncols) gd_cp4(vbuf + tok * (BC + 1) + c, row + 2 * G * d + h * a.dv + col0 + c);
+        else if (c == BC) gd_cp4(vbuf + tok * (BC + 1) + c, row + C + H * d + h);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
@@ -214,30 +215,36 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
 // addresses).  What a token's step costs is the chain of instructions that depend on the state: the staged vectors of the
 // NEXT token are read, and k * decay formed, while the current token's sums travel over the lanes; the decayed state
 // decay * S is formed beside the dot product (k * decay)^T S of the old state instead of before it; the read-out q^T S is
-// off the chain altogether.
-template <int RPT, bool VEC, int GD_R, bool DELTA>
+// off the chain altogether.  A thread holds its rows of NC columns (value channels): the columns are independent chains that
+// share the staged vectors, so the instructions that fetch them and form k * decay are issued once for NC columns, and the
+// chains' latencies overlap; every column's arithmetic is the same whatever NC is.
+template <int RPT, bool VEC, int GD_R, bool DELTA, int NC>
 __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a, int n_buf) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float gd_smem[];
-    constexpr int R4 = RPT / 4;
+    constexpr int R4 = RPT / 4, BC = GD_COLS * NC;
     int d = a.d, dv = a.dv;
-    int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * GD_COLS, tid = threadIdx.x;
+    int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * BC, tid = threadIdx.x;
     int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
     if (t_end <= t_begin) return;
-    int ncols = min(GD_COLS, dv - col0);
+    int ncols = min(BC, dv - col0);
     constexpr bool delta = DELTA;              // false: the plain sum of outer products, whose write needs no dot product
-    int jj = tid / GD_R, g = tid % GD_R, j = col0 + jj;
-    bool owner = jj < ncols;
+    int jj = (tid / GD_R) * NC, g = tid % GD_R;          // this thread's columns: col0 + jj .. + NC - 1
+    bool owner[NC];
     float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * dv;
-    float S[RPT];
+    float S[NC][RPT];
 #pragma unroll
-    for (int m = 0; m < RPT; ++m) {
-        int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
-        S[m] = (owner && row < d) ? sp[(size_t)row * dv + j] : 0.f;
+    for (int n = 0; n < NC; ++n) {
+        owner[n] = jj + n < ncols;
+#pragma unroll
+        for (int m = 0; m < RPT; ++m) {
+            int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+            S[n][m] = (owner[n] && row < d) ? sp[(size_t)row * dv + col0 + jj + n] : 0.f;
+        }
     }
     // a row of the staged vectors is padded to GD_R * RPT floats, so that every thread reads whole float4
     constexpr int dp = GD_R * RPT;
-    int buf_floats = 3 * GD_TILE * dp + GD_TILE * (GD_COLS + 1);
+    int buf_floats = 3 * GD_TILE * dp + GD_TILE * (BC + 1);
     buf_floats = (buf_floats + 3) / 4 * 4;
     // the padding of every staged row stays zero (rows of tokens a tile does not have are read ahead but never used)
     if (dp > d)
@@ -247,24 +254,24 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
         }
     __syncthreads();
     int n_tiles = (t_end - t_begin + GD_TILE - 1) / GD_TILE;
-    gd_stage<dp, VEC>(a, gd_smem, t_begin, min(GD_TILE, t_end - t_begin), h, col0, ncols);
+    gd_stage<dp, VEC, BC>(a, gd_smem, t_begin, min(GD_TILE, t_end - t_begin), h, col0, ncols);
     for (int tile = 0; tile < n_tiles; ++tile) {
         int t0 = t_begin + tile * GD_TILE, n_tok = min(GD_TILE, t_end - t0);
         float* buf = gd_smem + (tile & (n_buf - 1)) * buf_floats;
         if (tile + 1 < n_tiles && n_buf == 2) {
-            gd_stage<dp, VEC>(a, gd_smem + ((tile + 1) & 1) * buf_floats, t0 + GD_TILE, min(GD_TILE, t_end - t0 - GD_TILE), h, col0, ncols);
+            gd_stage<dp, VEC, BC>(a, gd_smem + ((tile + 1) & 1) * buf_floats, t0 + GD_TILE, min(GD_TILE, t_end - t0 - GD_TILE), h, col0, ncols);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
-            if (tile > 0 && n_buf == 1) gd_stage<dp, VEC>(a, buf, t0, n_tok, h, col0, ncols);     // one buffer: a tile is staged when its turn comes
+            if (tile > 0 && n_buf == 1) gd_stage<dp, VEC, BC>(a, buf, t0, n_tok, h, col0, ncols);     // one buffer: a tile is staged when its turn comes
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
         const float* vbuf = buf + 3 * GD_TILE * dp;
         // The sum over rows of S^T q is not needed by the next token: every thread keeps its part for each token of
         // the tile, and the butterflies of all tokens run together after the walk (their latencies overlap).
-        float part[GD_TILE];
+        float part[NC][GD_TILE];
         float4 w[R4], kw[R4], k[R4], q[R4];
-        float vj, beta;
+        float vj[NC], beta;
         auto lo2 = [](const float4& v) { return make_float2(v.x, v.y); };
         auto hi2 = [](const float4& v) { return make_float2(v.z, v.w); };
         auto fetch = [&](int tok) {                 // a token's vectors; nothing here depends on the state
@@ -276,73 +283,103 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
                 float2 a0 = __fmul2_rn(lo2(k[m]), lo2(w[m])), a1 = __fmul2_rn(hi2(k[m]), hi2(w[m]));
                 kw[m] = make_float4(a0.x, a0.y, a1.x, a1.y);
             }
-            vj = owner ? vbuf[tok * (GD_COLS + 1) + jj] : 0.f;
-            beta = vbuf[tok * (GD_COLS + 1) + GD_COLS];
+#pragma unroll
+            for (int n = 0; n < NC; ++n) vj[n] = owner[n] ? vbuf[tok * (BC + 1) + jj + n] : 0.f;
+            beta = vbuf[tok * (BC + 1) + BC];
         };
         fetch(0);
         // The arithmetic on the state runs on pairs of rows (fma.f32x2: two IEEE operations an instruction, the same results):
         // a token's step is a chain of instructions a warp issues nearly one after another, so their number is its time.
 #pragma unroll
         for (int tok = 0; tok < GD_TILE; ++tok) {
-            part[tok] = 0.f;
+#pragma unroll
+            for (int n = 0; n < NC; ++n) part[n][tok] = 0.f;
             if (tok < n_tok) {
                 // (k * decay)^T S over this thread's rows in four runs (a fixed order), and the decayed state beside it
-                float2 p01 = make_float2(0.f, 0.f), p23 = make_float2(0.f, 0.f);
-                float2 dS[RPT / 2];
+                float2 dS[NC][RPT / 2];
+                float dot[NC];
                 float4 kc[R4], qc[R4];
 #pragma unroll
-                for (int m = 0; m < R4; ++m) {
-                    float2 s01 = make_float2(S[4 * m], S[4 * m + 1]), s23 = make_float2(S[4 * m + 2], S[4 * m + 3]);
-                    if (delta) {
-                        p01 = __ffma2_rn(lo2(kw[m]), s01, p01);
-                        p23 = __ffma2_rn(hi2(kw[m]), s23, p23);
+                for (int m = 0; m < R4; ++m) { kc[m] = k[m]; qc[m] = q[m]; }
+#pragma unroll
+                for (int n = 0; n < NC; ++n) {
+                    float2 p01 = make_float2(0.f, 0.f), p23 = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int m = 0; m < R4; ++m) {
+                        float2 s01 = make_float2(S[n][4 * m], S[n][4 * m + 1]), s23 = make_float2(S[n][4 * m + 2], S[n][4 * m + 3]);
+                        if (delta) {
+                            p01 = __ffma2_rn(lo2(kw[m]), s01, p01);
+                            p23 = __ffma2_rn(hi2(kw[m]), s23, p23);
+                        }
+                        dS[n][2 * m] = __fmul2_rn(lo2(w[m]), s01);
+                        dS[n][2 * m + 1] = __fmul2_rn(hi2(w[m]), s23);
                     }
-                    dS[2 * m] = __fmul2_rn(lo2(w[m]), s01);
-                    dS[2 * m + 1] = __fmul2_rn(hi2(w[m]), s23);
-                    kc[m] = k[m]; qc[m] = q[m];
+                    dot[n] = (p01.x + p01.y) + (p23.x + p23.y);
                 }
-                float dot = (p01.x + p01.y) + (p23.x + p23.y);
-                const float v_now = vj, beta_now = beta;
+                float v_now[NC];
+#pragma unroll
+                for (int n = 0; n < NC; ++n) v_now[n] = vj[n];
+                const float beta_now = beta;
                 if (tok + 1 < GD_TILE) fetch(tok + 1);          // (rows past the tile's tokens hold older tokens: unused)
                 // over the column's lanes in rounds of four: every lane adds the same pairs, so all hold the same sum
                 if (delta) {
-                    float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
-                          e3 = __shfl_xor_sync(0xffffffffu, dot, 3);
-                    dot = (dot + e1) + (e2 + e3);
-                    float f1 = __shfl_xor_sync(0xffffffffu, dot, 4), f2 = __shfl_xor_sync(0xffffffffu, dot, 8),
-                          f3 = __shfl_xor_sync(0xffffffffu, dot, 12);
-                    dot = (dot + f1) + (f2 + f3);
-                    if (GD_R == 32) dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-                }
-                float u = delta ? beta_now * (v_now - dot) : v_now;         // the plain sum of outer products writes v itself
-                const float2 uu = make_float2(u, u);
-                float2 q01 = make_float2(0.f, 0.f), q23 = make_float2(0.f, 0.f);
+                    float e1[NC], e2[NC], e3[NC];
 #pragma unroll
-                for (int m = 0; m < R4; ++m) {
-                    float2 s01 = __ffma2_rn(lo2(kc[m]), uu, dS[2 * m]), s23 = __ffma2_rn(hi2(kc[m]), uu, dS[2 * m + 1]);
-                    S[4 * m] = s01.x; S[4 * m + 1] = s01.y; S[4 * m + 2] = s23.x; S[4 * m + 3] = s23.y;
-                    q01 = __ffma2_rn(s01, lo2(qc[m]), q01);
-                    q23 = __ffma2_rn(s23, hi2(qc[m]), q23);
+                    for (int n = 0; n < NC; ++n) {
+                        e1[n] = __shfl_xor_sync(0xffffffffu, dot[n], 1); e2[n] = __shfl_xor_sync(0xffffffffu, dot[n], 2);
+                        e3[n] = __shfl_xor_sync(0xffffffffu, dot[n], 3);
+                    }
+#pragma unroll
+                    for (int n = 0; n < NC; ++n) dot[n] = (dot[n] + e1[n]) + (e2[n] + e3[n]);
+#pragma unroll
+                    for (int n = 0; n < NC; ++n) {
+                        e1[n] = __shfl_xor_sync(0xffffffffu, dot[n], 4); e2[n] = __shfl_xor_sync(0xffffffffu, dot[n], 8);
+                        e3[n] = __shfl_xor_sync(0xffffffffu, dot[n], 12);
+                    }
+#pragma unroll
+                    for (int n = 0; n < NC; ++n) dot[n] = (dot[n] + e1[n]) + (e2[n] + e3[n]);
+                    if (GD_R == 32) {
+#pragma unroll
+                        for (int n = 0; n < NC; ++n) dot[n] += __shfl_xor_sync(0xffffffffu, dot[n], 16);
+                    }
                 }
-                part[tok] = (q01.x + q01.y) + (q23.x + q23.y);
+#pragma unroll
+                for (int n = 0; n < NC; ++n) {
+                    float u = delta ? beta_now * (v_now[n] - dot[n]) : v_now[n];         // the plain sum of outer products writes v itself
+                    const float2 uu = make_float2(u, u);
+                    float2 q01 = make_float2(0.f, 0.f), q23 = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int m = 0; m < R4; ++m) {
+                        float2 s01 = __ffma2_rn(lo2(kc[m]), uu, dS[n][2 * m]), s23 = __ffma2_rn(hi2(kc[m]), uu, dS[n][2 * m + 1]);
+                        S[n][4 * m] = s01.x; S[n][4 * m + 1] = s01.y; S[n][4 * m + 2] = s23.x; S[n][4 * m + 3] = s23.y;
+                        q01 = __ffma2_rn(s01, lo2(qc[m]), q01);
+                        q23 = __ffma2_rn(s23, hi2(qc[m]), q23);
+                    }
+                    part[n][tok] = (q01.x + q01.y) + (q23.x + q23.y);
+                }
             }
         }
 #pragma unroll
-        for (int o = 1; o < GD_R; o <<= 1)
+        for (int n = 0; n < NC; ++n) {
 #pragma unroll
-            for (int tok = 0; tok < GD_TILE; ++tok) part[tok] += __shfl_xor_sync(0xffffffffu, part[tok], o);
-        // lane g of a column stores token g of the tile (GD_TILE <= GD_R)
-        float mine = part[0];
+            for (int o = 1; o < GD_R; o <<= 1)
 #pragma unroll
-        for (int tok = 1; tok < GD_TILE; ++tok) mine = g == tok ? part[tok] : mine;
-        if (owner && g < n_tok) a.raw[(size_t)(t0 + g) * a.H * dv + h * dv + j] = mine;
+                for (int tok = 0; tok < GD_TILE; ++tok) part[n][tok] += __shfl_xor_sync(0xffffffffu, part[n][tok], o);
+            // lane g of a column stores token g of the tile (GD_TILE <= GD_R)
+            float mine = part[n][0];
+#pragma unroll
+            for (int tok = 1; tok < GD_TILE; ++tok) mine = g == tok ? part[n][tok] : mine;
+            if (owner[n] && g < n_tok) a.raw[(size_t)(t0 + g) * a.H * dv + h * dv + col0 + jj + n] = mine;
+        }
         __syncthreads();             // the buffer is free for the tile after the next
     }
 #pragma unroll
-    for (int m = 0; m < RPT; ++m) {
-        int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
-        if (owner && row < d) sp[(size_t)row * dv + j] = S[m];
-    }
+    for (int n = 0; n < NC; ++n)
+#pragma unroll
+        for (int m = 0; m < RPT; ++m) {
+            int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+            if (owner[n] && row < d) sp[(size_t)row * dv + col0 + jj + n] = S[n][m];
+        }
 }
 
 // A step of single tokens (every sequence brings exactly one): the walk's arithmetic for one token, laid out for bandwidth.
@@ -469,24 +506,39 @@ __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
     }
 }
 
-// n_buf 1: a step of single tokens (every sequence has one tile): one staging buffer, twice the blocks an SM
-template <int RPT, int R>
-static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, int n_buf, cudaStream_t stream) {
-    size_t floats = 3 * GD_TILE * R * RPT + GD_TILE * (GD_COLS + 1);
+// n_buf 1: every sequence has one tile: one staging buffer, twice the blocks an SM.  nc: value channels a thread holds.
+template <int RPT, int R, int NC>
+static void gd_launch_walk_nc(const GatedDeltaArgs& a, int B, bool vec, int n_buf, cudaStream_t stream) {
+    constexpr int BC = GD_COLS * NC;
+    size_t floats = 3 * GD_TILE * R * RPT + GD_TILE * (BC + 1);
     size_t smem = (size_t)n_buf * ((floats + 3) / 4 * 4) * sizeof(float);
-    dim3 grid(a.H, B, (a.dv + GD_COLS - 1) / GD_COLS);
+    dim3 grid(a.H, B, (a.dv + BC - 1) / BC);
     ce_note("gated_delta_walk_kernel");
     auto go = [&](auto kernel) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         ce_launch(kernel, grid, R * GD_COLS, smem, stream, a, n_buf);
     };
     if (a.rule == 0) {
-        if (vec) go(gated_delta_walk_kernel<RPT, true, R, true>);
-        else go(gated_delta_walk_kernel<RPT, false, R, true>);
+        if (vec) go(gated_delta_walk_kernel<RPT, true, R, true, NC>);
+        else go(gated_delta_walk_kernel<RPT, false, R, true, NC>);
     } else {
-        if (vec) go(gated_delta_walk_kernel<RPT, true, R, false>);
-        else go(gated_delta_walk_kernel<RPT, false, R, false>);
+        if (vec) go(gated_delta_walk_kernel<RPT, true, R, false, NC>);
+        else go(gated_delta_walk_kernel<RPT, false, R, false, NC>);
     }
+}
+
+// Two value channels a thread where that still leaves three blocks for every two SMs (CE_DELTA_WALK_COLS=1 or 2 forces one or
+// two, for measurement).  A column's sums are the same either way, so the choice may follow the number of sequences.  Measured
+// on one 2,048-token prompt with heads of 128 x 128, four launches: 32 heads (256 blocks of two columns a thread) 3.49 -> 2.85 ms;
+// 16 heads (128 blocks) 2.45 -> 2.50 ms, where a block's chain of dependent instructions, not the issue rate, sets the time.
+template <int RPT, int R>
+static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, int n_buf, cudaStream_t stream) {
+    static int cols = getenv("CE_DELTA_WALK_COLS") ? atoi(getenv("CE_DELTA_WALK_COLS")) : 0;
+    bool fits = a.dv % (2 * GD_COLS) == 0;
+    long long blocks2 = (long long)a.H * B * (a.dv / (2 * GD_COLS));
+    bool two = cols == 0 ? fits && 2 * blocks2 >= 3LL * ce_sm_count() : cols >= 2 && fits;
+    if (two) gd_launch_walk_nc<RPT, R, 2>(a, B, vec, n_buf, stream);
+    else gd_launch_walk_nc<RPT, R, 1>(a, B, vec, n_buf, stream);
 }
 
 // Floats of a ``prep`` row for these sizes.

@@ -79,6 +79,64 @@ def test_delta_rule_kernels_with_a_decay_per_head(H, G, d, dv, K):
         assert rel_err(got, want) < 2e-5, b
 
 
+@pytest.mark.parametrize("delta_rule", [True, False])
+def test_the_walk_with_two_columns_a_thread_gives_the_same_bits(delta_rule):
+    """Four sequences in one step are enough blocks for the walk to give a thread two value channels; one sequence alone is
+    not.  A column's arithmetic does not depend on that: the rows and the states are equal bit for bit, and right."""
+    from carbon_engine_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    H, G, d, dv, n = 8, 4, 16, 128, 21
+    C = 2 * G * d + H * dv
+    ld = C + 2 * H + H * dv
+    a_log = torch.randn(H, generator=g) * 0.5 if delta_rule else 0.9 + 0.09 * torch.rand(H, generator=g)
+    dt_bias, norm_w, taps = torch.randn(H, generator=g) * 0.3, 1 + 0.1 * torch.randn(dv, generator=g), torch.randn(C, 1, generator=g) * 0.5
+    rows = [torch.randn(n, ld, generator=g) for _ in range(4)]
+
+    def run(which):
+        lengths = [n] * len(which)
+        seq, slot_t, starts = _step_arrays(lengths, list(range(len(which))))
+        proj = torch.cat([rows[i] for i in which]).cuda()
+        T = proj.shape[0]
+        state = torch.zeros(len(which), H, d, dv, device="cuda")
+        prep = torch.empty(T, ops.gated_delta_prep_width(H, G, d, dv), device="cuda")
+        raw, out = torch.empty(T, H * dv, device="cuda"), torch.empty(T, H * dv, device="cuda")
+        gz = proj[:, C + 2 * H:C + 2 * H + H * dv]
+        if delta_rule:
+            ops.gated_delta(proj, proj[:, C + H:C + 2 * H], gz, taps.cuda(), a_log.cuda(), dt_bias.cuda(), norm_w.cuda(), prep, raw, state,
+                            None, out, seq, slot_t, starts, len(which), 0, C, H, G, d, dv, 1, 1e-5, decay=ops.DECAY_PER_HEAD)
+        else:
+            ops.gated_delta(proj, None, gz, None, a_log.cuda(), None, None, prep, raw, state,
+                            None, out, seq, slot_t, starts, len(which), 0, 0, H, G, d, dv, 1, 1e-5, decay=ops.DECAY_CONSTANT, delta=False,
+                            rotation=(None, None, 0, None, None))
+        return out.cpu(), state.cpu()
+
+    ops.reset_kernel_counts()
+    together, states = run([0, 1, 2, 3])
+    for i in range(4):
+        alone, state = run([i])
+        assert torch.equal(alone, together[i * n:(i + 1) * n]) and torch.equal(state[0], states[i]), i
+    assert ops.kernel_counts().get("gated_delta_walk_kernel") == 5
+    # and right: sequence 2 against the plain walk
+    x = rows[2].double()
+    if delta_rule:
+        conv = plain.causal_conv_silu(x[:, :C], taps.double())
+        q = plain.unit(conv[:, :G * d].reshape(n, G, d)) * d ** -0.5
+        k = plain.unit(conv[:, G * d:2 * G * d].reshape(n, G, d))
+        v = conv[:, 2 * G * d:].reshape(n, H, dv)
+        beta = torch.sigmoid(x[:, C:C + H])
+        dec = torch.exp(-torch.exp(a_log.double()) * plain.softplus(x[:, C + H:C + 2 * H] + dt_bias.double()))
+        want = torch.stack([plain.delta_rule_walk(q[:, i // 2], k[:, i // 2], v[:, i], dec[:, i:i + 1].expand(-1, d), beta[:, i])
+                            for i in range(H)], dim=1)
+        want = plain.rms_norm(want, norm_w.double(), 1e-5).reshape(n, -1) * torch.sigmoid(x[:, C + 2 * H:C + 2 * H + H * dv])
+    else:
+        q = x[:, :G * d].reshape(n, G, d)
+        k = x[:, G * d:2 * G * d].reshape(n, G, d) * d ** -0.5
+        v = x[:, 2 * G * d:C].reshape(n, H, dv)
+        want = torch.stack([plain.retention_walk(q[:, i // 2], k[:, i // 2], v[:, i], float(a_log[i])) for i in range(H)], dim=1)
+        want = plain.rms_norm(want, None, 1e-5).reshape(n, -1) * torch.sigmoid(x[:, C + 2 * H:C + 2 * H + H * dv])
+    assert rel_err(together[2 * n:3 * n].numpy(), want.numpy()) < 2e-5
+
+
 @pytest.mark.parametrize("H, d, dv, rd", [(3, 12, 8, 8), (1, 9, 5, 0), (2, 64, 64, 64), (1, 136, 8, 20)])
 def test_retention_kernels(H, d, dv, rd):
     from carbon_engine_b200 import ops
