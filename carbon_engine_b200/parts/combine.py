@@ -74,7 +74,6 @@ class SummedMixers(Mixer):
         return LayerCacheView("state" if state is not None else "none", state=state, writes=cache.writes, extra=extra or None)
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache, accumulate: bool = True) -> None:
-        from .linear import ACCUM                   # noqa: F401  (the members' output products add into x)
         for i, m in enumerate(self.members):
             # the first member stores where the caller wants a stored result; the others add to it
             m.forward(ctx, h, x, self._view(i, cache), accumulate=accumulate or i > 0)
