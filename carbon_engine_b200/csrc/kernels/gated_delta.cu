@@ -218,8 +218,10 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
 // off the chain altogether.  A thread holds its rows of NC columns (value channels): the columns are independent chains that
 // share the staged vectors, so the instructions that fetch them and form k * decay are issued once for NC columns, and the
 // chains' latencies overlap; every column's arithmetic is the same whatever NC is.
+// (Registers: with one column a thread four blocks of 128 threads share an SM, as many as the grid of a long prompt brings; with
+// two columns the grid is half as large and a thread may hold twice the registers, which spares it the spills.)
 template <int RPT, bool VEC, int GD_R, bool DELTA, int NC>
-__global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a, int n_buf) {
+__global__ void __launch_bounds__(GD_R * GD_COLS, (NC == 1 ? 512 : 256) / (GD_R * GD_COLS)) gated_delta_walk_kernel(GatedDeltaArgs a, int n_buf) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float gd_smem[];
     constexpr int R4 = RPT / 4, BC = GD_COLS * NC;
